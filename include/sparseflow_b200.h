@@ -1,0 +1,278 @@
+/*
+ * sparseflow_b200 -- C ABI of the Blackwell (sm_100a) 2:4-sparse FFN path.
+ *
+ * Plain C, plain pointers and sizes.  Unless a function says otherwise every data pointer is a
+ * DEVICE pointer, every call is asynchronous on the given CUDA stream (`stream` is a cudaStream_t
+ * passed as void*, NULL = default stream) and returns an sfb200_status.  There is no CPU fallback:
+ * without a usable sm_100 device the compute entry points return SFB200_ERROR_CUDA.
+ *
+ * Three groups of entry points:
+ *   1. sfb200_*       the hot path itself (prune+compress, sparse GEMM, gated FFN)
+ *   2. sf_*           the reference's runtime selection API, same structs and semantics
+ *   3. sparseflow_*   the reference's "stable C ABI v1", whose compute calls are stubs upstream
+ *
+ * Each declaration cites the reference interface it stands in for (path:line in the reference
+ * tree).
+ */
+#ifndef SPARSEFLOW_B200_H
+#define SPARSEFLOW_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SFB200_API __attribute__((visibility("default")))
+
+/* ------------------------------------------------------------------ common ---------------- */
+
+typedef enum {
+  SFB200_SUCCESS = 0,
+  SFB200_ERROR_INVALID_ARGUMENT = 1,
+  SFB200_ERROR_OUT_OF_MEMORY = 2,
+  SFB200_ERROR_CUDA = 3,
+  SFB200_ERROR_NOT_SUPPORTED = 4,
+  SFB200_ERROR_TENSOR_MAP = 8,
+  SFB200_ERROR_DEVICE = 9 /* a kernel gave up on a bounded wait; see sfb200_device_status */
+} sfb200_status;
+
+typedef enum { SFB200_F16 = 0, SFB200_BF16 = 1 } sfb200_dtype;
+/* which element wins a magnitude tie inside a group of four */
+typedef enum { SFB200_TIE_HIGH = 0 /* reference behaviour */, SFB200_TIE_LOW = 1 } sfb200_tie;
+typedef enum { SFB200_ACT_NONE = 0, SFB200_ACT_RELU = 1, SFB200_ACT_SILU = 2, SFB200_ACT_GELU = 3 } sfb200_act;
+
+SFB200_API const char* sfb200_status_string(int status);
+SFB200_API int sfb200_version(void); /* major*10000 + minor*100 + patch */
+
+/* Bytes of the compressed-values buffer ([rows, K/2] 16-bit) and of the tiled metadata buffer
+ * (128x128 tiles of 2 KiB, rows and K rounded up to 128) for a rows x K weight. */
+SFB200_API size_t sfb200_values_bytes(int rows, int K);
+SFB200_API size_t sfb200_meta_bytes(int rows, int K);
+
+/* Synchronise the current device and return the device status word (0 = ok) of the kernels
+ * launched so far; the word is cleared.  Non-zero: (code << 8) | detail, code 1 = a bounded
+ * mbarrier wait ran out. */
+SFB200_API int sfb200_device_status(int* status_word);
+
+/* ------------------------------------------------------------------ 1. hot path ----------- */
+
+/*
+ * 2:4 magnitude prune + compress of dense[rows, K] (row pitch ld elements).
+ * Stands in for experiments/prune_24_cpu.py:17-28 (selection rule, values, code bytes),
+ * sparseflow/nn/sparseflow_linear.py:20-35 (prune_24_dense_weight) and the
+ * torch.sparse.to_sparse_semi_structured call sites sparseflow/fused_mlp.py:22,28,
+ * sparseflow/nn/sparseflow_linear.py:66, sparseflow/nn/sparseflow_mlp.py:62-76.
+ * Any of the four outputs may be NULL.  `meta` needs K % 16 == 0 and 16-byte aligned buffers.
+ *   values    [rows, K/2]   kept pair per group, index order
+ *   meta      sfb200_meta_bytes(rows, K) bytes, layout consumed by sfb200_sparse_gemm
+ *   ref_codes [rows, K/4]   uint8, the reference script's PAIR_TO_CODE byte per group
+ *   pruned    [rows, K]     pruned dense copy
+ */
+SFB200_API int sfb200_prune_compress_24(const void* dense, int rows, int K, int ld, int dtype,
+                                        int tie, void* values, void* meta, void* ref_codes,
+                                        void* pruned, void* stream);
+
+/*
+ * Same, for the fused gate|up weight of the gated FFN: reads gate[I, K] and up[I, K] and emits
+ * the 2*I-row matrix whose rows alternate in blocks of 16 (16 gate rows, the matching 16 up
+ * rows, ...), which is the row order sfb200_sparse_gemm_swiglu expects.  Replaces the
+ * torch.cat([gate, up]) + to_sparse_semi_structured of sparseflow/fused_mlp.py:16-24.
+ * I % 16 == 0.
+ */
+SFB200_API int sfb200_prune_compress_gate_up(const void* gate, const void* up, int I, int K, int ld,
+                                             int dtype, int tie, void* values, void* meta,
+                                             void* stream);
+
+/* is_valid_dev (device int) := 1 iff every group of four has <= 2 non-zeros.
+ * Device-pointer form of sparseflow_validate_2_4 (include/sparseflow/c_api.h:171-176). */
+SFB200_API int sfb200_validate_24(const void* w, int rows, int K, int ld, int* is_valid_dev,
+                                  void* stream);
+
+/* values + meta -> pruned dense [rows, K] (row pitch ld). */
+SFB200_API int sfb200_decompress_24(const void* values, const void* meta, int rows, int K,
+                                    void* dense, int ld, void* stream);
+
+/*
+ * Y[M, N] = act(X[M, K] . W[N, K]^T + bias), W given as (values, meta).  fp32 accumulate,
+ * output in `dtype`.  ldx / ldy are row pitches in elements.  K % 64 == 0, N % 8 == 0.
+ * Stands in for aten::_sparse_semi_structured_mm / torch.mm(x, Wsp.t()) / F.linear(x, Wsp) at
+ * sparseflow/nn/sparseflow_linear.py:123, sparseflow/nn/sparseflow_mlp.py:95,97,
+ * sparseflow/fused_mlp.py:54,60, and for sparseflow_sparse_gemm (c_api.h:151-160).
+ */
+SFB200_API int sfb200_sparse_gemm(const void* x, int ldx, const void* values, const void* meta,
+                                  void* y, int ldy, int M, int N, int K, int dtype,
+                                  const void* bias, int act, void* stream);
+
+/*
+ * H[M, I] = silu(X . Wg^T) * (X . Wu^T) with the fused gate|up weight produced by
+ * sfb200_prune_compress_gate_up (2*I rows).  One GEMM, SiLU.mul in the epilogue: replaces the
+ * fused GEMM + chunk + act*up of sparseflow/fused_mlp.py:77-83 and the Triton kernel
+ * sparseflow/kernels/fused_silu_mul.py:6-31.
+ */
+SFB200_API int sfb200_sparse_gemm_swiglu(const void* x, int ldx, const void* values_gu,
+                                         const void* meta_gu, void* h, int ldh, int M, int I, int K,
+                                         int dtype, void* stream);
+
+/* out[r, c] = silu(gate[r, c]) * up[r, c], fp32 math (sparseflow/kernels/fused_silu_mul.py:33-57).
+ * Unfused variant, kept for the dense branch of the shape gate. */
+SFB200_API int sfb200_silu_mul(const void* gate, int ld_gate, const void* up, int ld_up, void* out,
+                               int ld_out, int rows, int cols, int dtype, void* stream);
+
+/*
+ * Gated FFN forward, out[M, H] = down(silu(gate(x)) * up(x)) (+ down_bias):
+ * sparseflow/fused_mlp.py:63-98 (SparseFlowFusedMLP.forward) with both GEMMs sparse.
+ * `hidden` is caller-provided scratch of M * I elements.
+ */
+typedef struct {
+  int H;                 /* hidden size   (K of gate/up, N of down) */
+  int I;                 /* intermediate  (N of gate/up, K of down) */
+  int dtype;             /* sfb200_dtype */
+  const void* gu_values; /* fused gate|up weight, 2*I rows x H      */
+  const void* gu_meta;
+  const void* down_values; /* down weight, H rows x I               */
+  const void* down_meta;
+  const void* down_bias; /* [H] or NULL */
+} sfb200_ffn_weights;
+
+SFB200_API int sfb200_ffn_forward(const sfb200_ffn_weights* w, const void* x, int ldx, void* hidden,
+                                  void* out, int ldo, int M, void* stream);
+
+/*
+ * Same with HOST input and output buffers (pinned memory recommended): copies x to the device,
+ * runs the FFN, copies the result back, and synchronises the stream.  Device staging buffers are
+ * owned by the library, grown on demand and reused.  This is the call a host-side integration
+ * without its own device buffers makes.
+ */
+SFB200_API int sfb200_ffn_forward_host(const sfb200_ffn_weights* w, const void* x_host,
+                                       void* out_host, int M, void* stream);
+
+/* ------------------------------------------------------------------ 2. sf_* runtime API --- */
+/* experiments/old_structure/runtime/api/sparseflow_api.h:8-28, exercised by tests/test_c_api.cpp. */
+
+typedef struct {
+  int32_t M, N, K;
+  int32_t dtype;          /* 0 f16, 1 bf16, 2 f32   (runtime/benchmark/micro_bench.h:8)  */
+  int32_t sparsity_type;  /* 0 dense, 1 2:4, 2 4:8  (micro_bench.h:9)                    */
+  float sparsity_ratio;
+  int32_t layout;         /* 0 row, 1 col           (micro_bench.h:10)                   */
+} sf_matmul_desc;
+
+typedef struct {
+  int32_t sm_arch;
+  int32_t num_sms;
+  uint64_t shared_mem_kb;
+} sf_gpu_info;
+
+/* Kernel ids (micro_bench.h:20-25): 0 dense tensor-core, 1 hybrid, 2 sparse (tcgen05 prefill
+ * kernel here), 3 sparse alternative (small-M kernel here). */
+SFB200_API int32_t sf_select_kernel(const char* cache_path, const sf_matmul_desc* desc,
+                                    const sf_gpu_info* gpu);
+SFB200_API int32_t sf_cache_size(const char* cache_path);
+SFB200_API void sf_cache_clear(const char* cache_path);
+
+/* Additions behind the same cache (no counterpart upstream; they make the dispatcher's
+ * "compression cached" rule and failure quarantine reachable through the C ABI, which upstream
+ * only reaches from C++: runtime/dispatch/kernel_dispatcher.cpp:67-98,165-174). */
+SFB200_API void sf_note_compressed(const char* cache_path, const sf_matmul_desc* desc);
+SFB200_API void sf_record_sparse_failure(const char* cache_path, const sf_matmul_desc* desc,
+                                         const sf_gpu_info* gpu);
+SFB200_API int32_t sf_bucket_dimension(int32_t dim); /* kernel_dispatcher.cpp:16-28 */
+
+/* ------------------------------------------------------------------ 3. C ABI v1 ----------- */
+/* experiments/old_structure/include/sparseflow/c_api.h:38-200; src/runtime/context.cpp:78-300. */
+
+#define SPARSEFLOW_ABI_VERSION_MAJOR 1
+#define SPARSEFLOW_ABI_VERSION_MINOR 1 /* 1.1: adds SPARSEFLOW_DTYPE_BF16 */
+#define SPARSEFLOW_ABI_VERSION_PATCH 0
+
+typedef struct SparseFlowContext_* SparseFlowContext;
+typedef struct SparseFlowKernel_* SparseFlowKernel;
+
+typedef enum {
+  SPARSEFLOW_SUCCESS = 0,
+  SPARSEFLOW_ERROR_INVALID_ARGUMENT = 1,
+  SPARSEFLOW_ERROR_OUT_OF_MEMORY = 2,
+  SPARSEFLOW_ERROR_CUDA_ERROR = 3,
+  SPARSEFLOW_ERROR_NOT_SUPPORTED = 4,
+  SPARSEFLOW_ERROR_INVALID_HANDLE = 5,
+  SPARSEFLOW_ERROR_COMPILATION_FAILED = 6,
+  SPARSEFLOW_ERROR_ABI_MISMATCH = 7
+} SparseFlowStatus;
+
+typedef struct { int major; int minor; int patch; } SparseFlowVersion;
+
+typedef enum {
+  SPARSEFLOW_EPILOGUE_NONE = 0,
+  SPARSEFLOW_EPILOGUE_RELU = 1,
+  SPARSEFLOW_EPILOGUE_SILU = 2,
+  SPARSEFLOW_EPILOGUE_GELU = 3,
+  SPARSEFLOW_EPILOGUE_BIAS = 4,
+  SPARSEFLOW_EPILOGUE_BIAS_RELU = 5,
+  SPARSEFLOW_EPILOGUE_BIAS_SILU = 6
+} SparseFlowEpilogue;
+
+typedef struct {
+  SparseFlowEpilogue kind;
+  const void* params;  /* bias device pointer for the BIAS* kinds */
+  size_t params_size;
+} SparseFlowEpilogueConfig;
+
+typedef struct {
+  int tile_m, tile_n, tile_k; /* 0 = auto; tile_n in {32,64,128,192,256} picks the token tile */
+  SparseFlowEpilogueConfig epilogue;
+} SparseFlowKernelConfig;
+
+typedef enum {
+  SPARSEFLOW_DTYPE_FP16 = 0,
+  SPARSEFLOW_DTYPE_FP32 = 1,
+  SPARSEFLOW_DTYPE_INT8 = 2,
+  SPARSEFLOW_DTYPE_BF16 = 3
+} SparseFlowDataType;
+
+typedef struct {
+  double elapsed_ms;
+  double tflops_effective;
+  double tflops_real;
+  double bandwidth_gb_s;
+} SparseFlowBenchmarkResult;
+
+SFB200_API const char* sparseflow_get_error_string(SparseFlowStatus status);     /* c_api.h:58 */
+SFB200_API const char* sparseflow_get_last_error(void);                          /* c_api.h:61 */
+SFB200_API SparseFlowVersion sparseflow_get_version(void);                       /* c_api.h:73 */
+SFB200_API int sparseflow_is_abi_compatible(int major, int minor);               /* c_api.h:76 */
+SFB200_API SparseFlowStatus sparseflow_create_context(SparseFlowContext* ctx, int device_id); /* :83 */
+SFB200_API SparseFlowStatus sparseflow_destroy_context(SparseFlowContext ctx);   /* c_api.h:89 */
+SFB200_API SparseFlowStatus sparseflow_get_device_info(SparseFlowContext ctx, int* compute_capability,
+                                                       int* sm_count, size_t* total_memory); /* :94 */
+SFB200_API SparseFlowStatus sparseflow_compile_kernel(SparseFlowContext ctx, SparseFlowKernel* kernel,
+                                                      const SparseFlowKernelConfig* config); /* :131 */
+SFB200_API SparseFlowStatus sparseflow_destroy_kernel(SparseFlowKernel kernel);  /* c_api.h:138 */
+/*
+ * C[M, N] = epilogue(A[M, K] . W^T), W = N x K weight compressed by sparseflow_compress_2_4.
+ * `Bc` points at the compressed block: values (sfb200_values_bytes(N, K) bytes) followed, at the
+ * next 256-byte boundary, by the metadata.  c_api.h:151-160 (a stub upstream, context.cpp:248).
+ */
+SFB200_API SparseFlowStatus sparseflow_sparse_gemm(SparseFlowKernel kernel, const void* A,
+                                                   const void* Bc, void* C, int M, int N, int K,
+                                                   SparseFlowDataType dtype, void* stream);
+/* dense[M, N] -> compressed values + metadata; M rows, N = length of the pruned (K) axis.
+ * c_api.h:163-169.  Prunes by magnitude first (idempotent on an already 2:4 tensor). */
+SFB200_API SparseFlowStatus sparseflow_compress_2_4(SparseFlowContext ctx, const void* dense,
+                                                    void* compressed, void* metadata, int M, int N,
+                                                    SparseFlowDataType dtype);
+/* Synchronous; is_valid is a HOST int.  c_api.h:172-177. */
+SFB200_API SparseFlowStatus sparseflow_validate_2_4(const void* tensor, int M, int N,
+                                                    SparseFlowDataType dtype, int* is_valid);
+/* Times the sparse GEMM on library-owned synthetic buffers.  c_api.h:190-195. */
+SFB200_API SparseFlowStatus sparseflow_benchmark_kernel(SparseFlowKernel kernel, int M, int N, int K,
+                                                        int num_iterations,
+                                                        SparseFlowBenchmarkResult* result);
+/* Offset of the metadata inside the compressed block that sparseflow_sparse_gemm takes. */
+SFB200_API size_t sparseflow_compressed_meta_offset(int N, int K);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPARSEFLOW_B200_H */

@@ -1,0 +1,75 @@
+"""ctypes binding of libsparseflow_b200.so (the C ABI declared in include/sparseflow_b200.h).
+
+There is no fallback: if the library is missing the import of any compute function raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libsparseflow_b200.so")
+
+_lib = None
+
+
+class FFNWeights(C.Structure):
+    _fields_ = [
+        ("H", C.c_int), ("I", C.c_int), ("dtype", C.c_int),
+        ("gu_values", C.c_void_p), ("gu_meta", C.c_void_p),
+        ("down_values", C.c_void_p), ("down_meta", C.c_void_p),
+        ("down_bias", C.c_void_p),
+    ]
+
+
+class MatmulDesc(C.Structure):
+    _fields_ = [("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32), ("dtype", C.c_int32),
+                ("sparsity_type", C.c_int32), ("sparsity_ratio", C.c_float), ("layout", C.c_int32)]
+
+
+class GpuInfo(C.Structure):
+    _fields_ = [("sm_arch", C.c_int32), ("num_sms", C.c_int32), ("shared_mem_kb", C.c_uint64)]
+
+
+class SfbError(RuntimeError):
+    def __init__(self, fn: str, code: int):
+        msg = lib().sfb200_status_string(code).decode()
+        super().__init__(f"{fn} failed: {msg} (status {code})")
+        self.code = code
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m sparseflow_b200.build` "
+            "(there is no CPU or PyTorch fallback)")
+    L = C.CDLL(LIB_PATH)
+    vp, i, sz = C.c_void_p, C.c_int, C.c_size_t
+    L.sfb200_status_string.restype = C.c_char_p
+    L.sfb200_status_string.argtypes = [i]
+    L.sfb200_version.restype = i
+    L.sfb200_values_bytes.restype = sz
+    L.sfb200_values_bytes.argtypes = [i, i]
+    L.sfb200_meta_bytes.restype = sz
+    L.sfb200_meta_bytes.argtypes = [i, i]
+    L.sfb200_device_status.argtypes = [C.POINTER(C.c_int)]
+    L.sfb200_prune_compress_24.argtypes = [vp, i, i, i, i, i, vp, vp, vp, vp, vp]
+    L.sfb200_prune_compress_gate_up.argtypes = [vp, vp, i, i, i, i, i, vp, vp, vp]
+    L.sfb200_validate_24.argtypes = [vp, i, i, i, vp, vp]
+    L.sfb200_decompress_24.argtypes = [vp, vp, i, i, vp, i, vp]
+    L.sfb200_sparse_gemm.argtypes = [vp, i, vp, vp, vp, i, i, i, i, i, vp, i, vp]
+    L.sfb200_sparse_gemm_swiglu.argtypes = [vp, i, vp, vp, vp, i, i, i, i, i, vp]
+    L.sfb200_silu_mul.argtypes = [vp, i, vp, i, vp, i, i, i, i, vp]
+    L.sfb200_ffn_forward.argtypes = [C.POINTER(FFNWeights), vp, i, vp, vp, i, i, vp]
+    L.sfb200_ffn_forward_host.argtypes = [C.POINTER(FFNWeights), vp, vp, i, vp]
+    L.sfb200_debug_force_token_tile.argtypes = [i]
+    _lib = L
+    return L
+
+
+def check(fn: str, code: int) -> None:
+    if code != 0:
+        raise SfbError(fn, code)

@@ -1,0 +1,256 @@
+// C-ABI entry points of the hot path (group 1 of include/sparseflow_b200.h).
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+
+#include "../../include/sparseflow_b200.h"
+#include "device_state.h"
+#include "kernels.h"
+
+using namespace sfb200;
+
+namespace sfb200 {
+
+static DeviceState g_states[kMaxDevices];
+static std::mutex g_state_mu;
+
+DeviceState* device_state(int* err) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    if (err) *err = kErrCuda;
+    cudaGetLastError();
+    return nullptr;
+  }
+  DeviceState* s = &g_states[dev];
+  if (s->ready) return s;
+  std::lock_guard<std::mutex> lk(g_state_mu);
+  if (s->ready) return s;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) {
+    if (err) *err = kErrCuda;
+    cudaGetLastError();
+    return nullptr;
+  }
+  s->cc = prop.major * 10 + prop.minor;
+  s->num_sms = prop.multiProcessorCount;
+  s->total_mem = prop.totalGlobalMem;
+  if (prop.major != 10) {  // kernels are sm_100a only
+    if (err) *err = kErrNotSupported;
+    return nullptr;
+  }
+  if (cudaMalloc(&s->status, 256) != cudaSuccess || cudaMemset(s->status, 0, 256) != cudaSuccess) {
+    if (err) *err = kErrOutOfMemory;
+    cudaGetLastError();
+    return nullptr;
+  }
+  s->ready = true;
+  return s;
+}
+
+}  // namespace sfb200
+
+extern "C" {
+
+const char* sfb200_status_string(int status) {
+  switch (status) {
+    case SFB200_SUCCESS: return "success";
+    case SFB200_ERROR_INVALID_ARGUMENT: return "invalid argument";
+    case SFB200_ERROR_OUT_OF_MEMORY: return "out of device memory";
+    case SFB200_ERROR_CUDA: return "CUDA error (no usable device, or a launch failed)";
+    case SFB200_ERROR_NOT_SUPPORTED: return "not supported (needs an sm_100 device)";
+    case SFB200_ERROR_TENSOR_MAP: return "TMA tensor map could not be encoded";
+    case SFB200_ERROR_DEVICE: return "device-side failure (bounded wait ran out)";
+    default: return "unknown status";
+  }
+}
+
+int sfb200_version(void) { return 100; }
+
+size_t sfb200_values_bytes(int rows, int K) { return values_bytes(rows, K); }
+size_t sfb200_meta_bytes(int rows, int K) { return meta_bytes(rows, K); }
+
+int sfb200_device_status(int* status_word) {
+  int err = kOk;
+  DeviceState* s = device_state(&err);
+  if (!s) return err;
+  if (cudaDeviceSynchronize() != cudaSuccess) return kErrCuda;
+  int w = 0;
+  if (cudaMemcpy(&w, s->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return kErrCuda;
+  if (w != 0) cudaMemset(s->status, 0, sizeof(int));
+  if (status_word) *status_word = w;
+  return w == 0 ? kOk : kErrDevice;
+}
+
+int sfb200_prune_compress_24(const void* dense, int rows, int K, int ld, int dtype, int tie,
+                             void* values, void* meta, void* ref_codes, void* pruned, void* stream) {
+  int err = kOk;
+  if (!device_state(&err)) return err;
+  PruneArgs a{};
+  a.dense = dense;
+  a.rows = rows;
+  a.K = K;
+  a.ld = ld;
+  a.fmt = dtype;
+  a.tie = tie;
+  a.values = values;
+  a.meta = meta;
+  a.ref_codes = ref_codes;
+  a.pruned = pruned;
+  return launch_prune_compress(a, static_cast<cudaStream_t>(stream));
+}
+
+int sfb200_prune_compress_gate_up(const void* gate, const void* up, int I, int K, int ld, int dtype,
+                                  int tie, void* values, void* meta, void* stream) {
+  int err = kOk;
+  if (!device_state(&err)) return err;
+  if (gate == nullptr || up == nullptr || I % 16 != 0) return kErrInvalid;
+  PruneArgs a{};
+  a.dense = gate;
+  a.dense2 = up;
+  a.rows = I;
+  a.K = K;
+  a.ld = ld;
+  a.fmt = dtype;
+  a.tie = tie;
+  a.interleave = 16;
+  a.values = values;
+  a.meta = meta;
+  return launch_prune_compress(a, static_cast<cudaStream_t>(stream));
+}
+
+int sfb200_validate_24(const void* w, int rows, int K, int ld, int* is_valid_dev, void* stream) {
+  int err = kOk;
+  if (!device_state(&err)) return err;
+  if (w == nullptr || is_valid_dev == nullptr) return kErrInvalid;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int one = 1;
+  if (cudaMemcpyAsync(is_valid_dev, &one, sizeof(int), cudaMemcpyHostToDevice, st) != cudaSuccess)
+    return kErrCuda;
+  return launch_validate_24(w, rows, K, ld, is_valid_dev, st);
+}
+
+int sfb200_decompress_24(const void* values, const void* meta, int rows, int K, void* dense, int ld,
+                         void* stream) {
+  int err = kOk;
+  if (!device_state(&err)) return err;
+  if (!values || !meta || !dense) return kErrInvalid;
+  return launch_decompress(values, meta, rows, K, dense, ld, static_cast<cudaStream_t>(stream));
+}
+
+static int run_gemm(DeviceState* s, const void* x, int ldx, const void* values, const void* meta,
+                    void* y, int ldy, int M, int N, int K, int dtype, const void* bias, int act,
+                    int epi, int force_bn, cudaStream_t st) {
+  if (!x || !values || !meta || !y) return kErrInvalid;
+  if (dtype != kF16 && dtype != kBF16) return kErrInvalid;
+  SparseGemmArgs a{};
+  a.x = x;
+  a.values = values;
+  a.meta = meta;
+  a.y = y;
+  a.bias = bias;
+  a.status = s->status;
+  a.m_tok = M;
+  a.n_out = N;
+  a.K = K;
+  a.ldx = ldx;
+  a.ldy = ldy;
+  a.fmt = dtype;
+  a.epi = epi;
+  a.act = act;
+  a.num_sms = s->num_sms;
+  a.force_bn = force_bn ? force_bn : s->force_bn;
+  return launch_sparse_gemm(a, st);
+}
+
+int sfb200_sparse_gemm(const void* x, int ldx, const void* values, const void* meta, void* y,
+                       int ldy, int M, int N, int K, int dtype, const void* bias, int act,
+                       void* stream) {
+  int err = kOk;
+  DeviceState* s = device_state(&err);
+  if (!s) return err;
+  return run_gemm(s, x, ldx, values, meta, y, ldy, M, N, K, dtype, bias, act, kEpiStore, 0,
+                  static_cast<cudaStream_t>(stream));
+}
+
+int sfb200_sparse_gemm_swiglu(const void* x, int ldx, const void* values_gu, const void* meta_gu,
+                              void* h, int ldh, int M, int I, int K, int dtype, void* stream) {
+  int err = kOk;
+  DeviceState* s = device_state(&err);
+  if (!s) return err;
+  return run_gemm(s, x, ldx, values_gu, meta_gu, h, ldh, M, 2 * I, K, dtype, nullptr, kActNone,
+                  kEpiSwiGLU, 0, static_cast<cudaStream_t>(stream));
+}
+
+int sfb200_silu_mul(const void* gate, int ld_gate, const void* up, int ld_up, void* out, int ld_out,
+                    int rows, int cols, int dtype, void* stream) {
+  int err = kOk;
+  if (!device_state(&err)) return err;
+  return launch_silu_mul(gate, up, out, rows, cols, ld_gate, ld_up, ld_out, dtype,
+                         static_cast<cudaStream_t>(stream));
+}
+
+int sfb200_ffn_forward(const sfb200_ffn_weights* w, const void* x, int ldx, void* hidden, void* out,
+                       int ldo, int M, void* stream) {
+  int err = kOk;
+  DeviceState* s = device_state(&err);
+  if (!s) return err;
+  if (!w || !hidden) return kErrInvalid;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = run_gemm(s, x, ldx, w->gu_values, w->gu_meta, hidden, w->I, M, 2 * w->I, w->H, w->dtype,
+                    nullptr, kActNone, kEpiSwiGLU, 0, st);
+  if (rc != kOk) return rc;
+  return run_gemm(s, hidden, w->I, w->down_values, w->down_meta, out, ldo, M, w->H, w->I, w->dtype,
+                  w->down_bias, kActNone, kEpiStore, 0, st);
+}
+
+int sfb200_ffn_forward_host(const sfb200_ffn_weights* w, const void* x_host, void* out_host, int M,
+                            void* stream) {
+  int err = kOk;
+  DeviceState* s = device_state(&err);
+  if (!s) return err;
+  if (!w || !x_host || !out_host || M <= 0) return kErrInvalid;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t xb = static_cast<size_t>(M) * w->H * 2, hb = static_cast<size_t>(M) * w->I * 2;
+  {
+    std::lock_guard<std::mutex> lk(g_state_mu);
+    if (s->stage_x_bytes < xb) {
+      if (s->stage_x) cudaFree(s->stage_x);
+      if (s->stage_o) cudaFree(s->stage_o);
+      s->stage_x = s->stage_o = nullptr;
+      s->stage_x_bytes = 0;
+      if (cudaMalloc(&s->stage_x, xb) != cudaSuccess || cudaMalloc(&s->stage_o, xb) != cudaSuccess) {
+        cudaGetLastError();
+        return kErrOutOfMemory;
+      }
+      s->stage_x_bytes = xb;
+    }
+    if (s->stage_h_bytes < hb) {
+      if (s->stage_h) cudaFree(s->stage_h);
+      s->stage_h = nullptr;
+      s->stage_h_bytes = 0;
+      if (cudaMalloc(&s->stage_h, hb) != cudaSuccess) {
+        cudaGetLastError();
+        return kErrOutOfMemory;
+      }
+      s->stage_h_bytes = hb;
+    }
+  }
+  if (cudaMemcpyAsync(s->stage_x, x_host, xb, cudaMemcpyHostToDevice, st) != cudaSuccess) return kErrCuda;
+  int rc = sfb200_ffn_forward(w, s->stage_x, w->H, s->stage_h, s->stage_o, w->H, M, stream);
+  if (rc != kOk) return rc;
+  if (cudaMemcpyAsync(out_host, s->stage_o, xb, cudaMemcpyDeviceToHost, st) != cudaSuccess) return kErrCuda;
+  if (cudaStreamSynchronize(st) != cudaSuccess) return kErrCuda;
+  return kOk;
+}
+
+/* Test / tuning hook: force the token tile of the tcgen05 kernel (0 = automatic). */
+SFB200_API int sfb200_debug_force_token_tile(int bn) {
+  int err = kOk;
+  DeviceState* s = device_state(&err);
+  if (!s) return err;
+  s->force_bn = bn;
+  return kOk;
+}
+
+}  // extern "C"

@@ -1,0 +1,27 @@
+// Per-device library state: status word, device facts, staging buffers of the host-buffer FFN call.
+#pragma once
+#include <stddef.h>
+
+namespace sfb200 {
+
+constexpr int kMaxDevices = 16;
+
+struct DeviceState {
+  bool ready = false;
+  int cc = 0;
+  int num_sms = 0;
+  size_t total_mem = 0;
+  int* status = nullptr;       // device status word (256-byte allocation, word 0 used)
+  int force_bn = 0;            // tuning hook: token tile override
+  void* stage_x = nullptr;     // host-buffer FFN: device copies of x / out, hidden scratch
+  void* stage_o = nullptr;
+  void* stage_h = nullptr;
+  size_t stage_x_bytes = 0;
+  size_t stage_h_bytes = 0;
+};
+
+// State of the current device, created on first use.  Returns nullptr and sets *err when there is
+// no usable sm_100 device.
+DeviceState* device_state(int* err);
+
+}  // namespace sfb200

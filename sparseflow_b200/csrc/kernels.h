@@ -1,0 +1,78 @@
+// Internal launch interface between the C-ABI layer and the CUDA kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace sfb200 {
+
+enum Err : int {
+  kOk = 0,
+  kErrInvalid = 1,
+  kErrOutOfMemory = 2,
+  kErrCuda = 3,
+  kErrNotSupported = 4,
+  kErrTensorMap = 8,
+  kErrDevice = 9,     // a kernel reported a device-side failure through the status word
+};
+
+enum Fmt : int { kF16 = 0, kBF16 = 1 };
+enum Epi : int { kEpiStore = 0, kEpiSwiGLU = 1 };
+enum Act : int { kActNone = 0, kActRelu = 1, kActSilu = 2, kActGelu = 3 };
+enum Tie : int { kTieHigh = 0, kTieLow = 1 };
+
+// ---- prune + compress --------------------------------------------------------------------
+struct PruneArgs {
+  const void* dense;      // [rows, K] 16-bit, row pitch ld elements
+  const void* dense2;     // optional second source (gate|up fusion), same shape, or null
+  int rows;               // rows of ONE source
+  int K;
+  int ld;
+  int fmt;
+  int tie;
+  int interleave;         // 0: out row r <- dense[r].  B>0 (needs dense2): blocks of B rows of
+                          // `dense` followed by the matching B rows of `dense2`; out rows = 2*rows
+  void* values;           // [out_rows, K/2]            or null
+  void* meta;             // tiled metadata             or null
+  void* ref_codes;        // [out_rows, K/4] uint8      or null
+  void* pruned;           // [out_rows, K]              or null
+};
+int launch_prune_compress(const PruneArgs& a, cudaStream_t stream);
+// one int result: 1 if every group of four has <= 2 non-zeros
+int launch_validate_24(const void* w, int rows, int K, int ld, int* d_flag, cudaStream_t stream);
+// rebuild pruned-dense [rows, K] from values + tiled metadata
+int launch_decompress(const void* values, const void* meta, int rows, int K, void* dense, int ld,
+                      cudaStream_t stream);
+
+inline size_t values_bytes(int rows, int K) { return static_cast<size_t>(rows) * (K / 2) * 2; }
+inline size_t meta_bytes(int rows, int K) {
+  return static_cast<size_t>((rows + 127) / 128) * ((K + 127) / 128) * 2048;
+}
+
+// ---- sparse GEMM ---------------------------------------------------------------------------
+struct SparseGemmArgs {
+  const void* x;          // [m_tok, K], row pitch ldx
+  const void* values;     // [n_out, K/2]
+  const void* meta;       // tiled metadata of the n_out x K weight
+  void* y;                // kEpiStore: [m_tok, n_out];  kEpiSwiGLU: [m_tok, n_out/2]; pitch ldy
+  const void* bias;       // [n_out] or null (kEpiStore only)
+  int* status;            // device status word
+  int m_tok, n_out, K;
+  int ldx, ldy;
+  int fmt;
+  int epi;
+  int act;
+  int num_sms;
+  int force_bn;           // 0 = choose by token count
+};
+int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream);
+
+// ---- small-M (decode) sparse GEMM ----------------------------------------------------------
+int launch_sparse_gemm_small_m(const SparseGemmArgs& a, cudaStream_t stream);
+
+// ---- elementwise -----------------------------------------------------------------------------
+// out[m, i] = silu(gu[m, i]) * gu[m, I + i]   (unfused variant, gate|up concatenated along columns)
+int launch_silu_mul(const void* gate, const void* up, void* out, int rows, int cols, int ld_g,
+                    int ld_u, int ld_o, int fmt, cudaStream_t stream);
+
+}  // namespace sfb200

@@ -1,0 +1,422 @@
+// 2:4-sparse GEMM for sm_100a:  Y[tokens, out] = X[tokens, K] . W[out, K]^T  with W held as
+// compressed values [out, K/2] + tiled 2-bit metadata (layout: see prune_compress.cu).
+//
+// Replaces the reference's sparse matmul call sites (sparseflow/fused_mlp.py:54,60,
+// sparseflow/nn/sparseflow_linear.py:123, sparseflow/nn/sparseflow_mlp.py:95,97), which go to
+// PyTorch's Ampere semi-structured kernels, and the fused SiLU.mul of
+// sparseflow/kernels/fused_silu_mul.py:6-31 (here an epilogue of the gate|up GEMM).
+//
+// Mapping onto tcgen05.mma.sp (kind::f16, fp32 accumulate in tensor memory):
+//   MMA A operand (sparse, M=128 rows)  = 128 weight rows, K-major compressed values in smem
+//   MMA B operand (dense,  N=BN rows)   = BN tokens of X, K-major in smem
+//   MMA D (128 lanes x BN columns fp32) = Y^T tile: lane = out feature, column = token
+//   metadata: 128 lanes x 1 column per K=32 instruction, copied smem -> tmem with tcgen05.cp
+//
+// One persistent CTA per SM, 6 warps: warp 0 = TMA producer, warp 1 = MMA issuer (one thread) and
+// tensor-memory owner, warps 2..5 = epilogue (tmem -> registers -> smem -> TMA store).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "kernels.h"
+#include "sm100_ptx.cuh"
+
+namespace sfb200 {
+
+namespace {
+
+struct GemmParams {
+  const uint32_t* meta;   // [row_tiles][k_tiles][128][4]
+  const void* bias;       // per out feature, 16-bit type, or null
+  int* status;            // device status word
+  int n_out;              // weight rows
+  int m_tok;              // tokens
+  int K;                  // logical K
+  int k_tiles128;         // ceil(K / 128): metadata tiles along K
+  int num_m_blks;         // ceil(n_out / 128)
+  int num_n_blks;         // ceil(m_tok / BN)
+  int fmt;                // 0 = f16, 1 = bf16
+  int act;                // Activation for EPI_STORE
+};
+
+template <int BN_, int BK_, int STAGES_, int EPI_>
+struct Cfg {
+  static constexpr int BM = 128;
+  static constexpr int BN = BN_;
+  static constexpr int BK = BK_;
+  static constexpr int STAGES = STAGES_;
+  static constexpr int EPI = EPI_;
+  static constexpr int A_BYTES = BM * (BK / 2) * 2;
+  static constexpr int B_SUBS = BK / 64;          // 64-element (128 B) wide sub tiles of X
+  static constexpr int B_SUB_BYTES = BN * 128;
+  static constexpr int B_BYTES = B_SUBS * B_SUB_BYTES;
+  static constexpr int E_BYTES = 2048;            // one 128x128 metadata tile
+  static constexpr int MMAS_PER_STAGE = BK / 32;
+  static constexpr int ACC_STAGES = (2 * BN + 4 * STAGES <= 512) ? 2 : 1;
+  static constexpr int TMEM_USED = ACC_STAGES * BN + 4 * STAGES;
+  static constexpr int TMEM_COLS = TMEM_USED <= 32 ? 32 : TMEM_USED <= 64 ? 64 : TMEM_USED <= 128 ? 128
+                                   : TMEM_USED <= 256 ? 256 : 512;
+  static constexpr int D_ROWS = 32;               // tokens per store chunk
+  static constexpr int D_COLS = (EPI == kEpiSwiGLU) ? 64 : 128;
+  static constexpr int D_BYTES = D_ROWS * D_COLS * 2;
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
+  static constexpr int OFF_E = OFF_B + STAGES * B_BYTES;
+  static constexpr int OFF_D = OFF_E + STAGES * E_BYTES;
+  static constexpr int OFF_BAR = OFF_D + 2 * D_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;  // + barriers + alignment slack
+  static_assert(BK == 64 || BK == 128, "BK");
+  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "BN");
+  static_assert(TMEM_USED <= 512, "tmem");
+  static_assert(SMEM_BYTES <= 232448, "smem");
+  static_assert(BK == 128 || STAGES % 2 == 0 || true, "");
+};
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  switch (act) {
+    case kActRelu: return fmaxf(v, 0.f);
+    case kActSilu: return v * __fdividef(1.f, 1.f + __expf(-v));
+    case kActGelu: return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+    default: return v;
+  }
+}
+
+__device__ __forceinline__ uint16_t to_bits16(float v, int fmt) {
+  if (fmt == 1) return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+  return __half_as_ushort(__float2half_rn(v));
+}
+__device__ __forceinline__ float from_bits16(uint16_t b, int fmt) {
+  if (fmt == 1) return __bfloat162float(__ushort_as_bfloat16(b));
+  return __half2float(__ushort_as_half(b));
+}
+
+template <class C>
+__global__ void __launch_bounds__(192, 1)
+sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t sbase = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  // barrier slots: full[S], empty[S], acc_full[2], acc_empty[2]
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * C::STAGES;
+  const uint32_t bar_accf = bar_empty + 8 * C::STAGES;
+  const uint32_t bar_acce = bar_accf + 8 * 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + 8 * (2 * C::STAGES + 4));
+  volatile int* err = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.num_m_blks * p.num_n_blks;
+  const int k_iters = (p.K + C::BK - 1) / C::BK;
+
+  if (threadIdx.x == 0) {
+    *err = 0;
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_accf + 8 * a, 1);
+      mbar_init(bar_acce + 8 * a, 4);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmD);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m_blk = tile / p.num_n_blks;
+        const int n_blk = tile % p.num_n_blks;
+        for (int kt = 0; kt < k_iters; ++kt) {
+          ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, err, p.status, 1);
+          if (!ok) break;
+          const bool load_e = (C::BK == 128) || ((kt & 1) == 0);
+          const uint32_t full = bar_full + 8 * s;
+          mbar_arrive_expect_tx(full, C::A_BYTES + C::B_BYTES + (load_e ? C::E_BYTES : 0));
+          tma_load_2d(sbase + C::OFF_A + s * C::A_BYTES, &tmA, kt * (C::BK / 2), m_blk * C::BM, full);
+#pragma unroll
+          for (int j = 0; j < C::B_SUBS; ++j)
+            tma_load_2d(sbase + C::OFF_B + s * C::B_BYTES + j * C::B_SUB_BYTES, &tmB,
+                        kt * C::BK + j * 64, n_blk * C::BN, full);
+          if (load_e) {
+            const int kt128 = (C::BK == 128) ? kt : (kt >> 1);
+            const uint32_t* src =
+                p.meta + (static_cast<size_t>(m_blk) * p.k_tiles128 + kt128) * 512;
+            bulk_load_1d(sbase + C::OFF_E + s * C::E_BYTES, src, C::E_BYTES, full);
+          }
+          if (++s == C::STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = make_idesc_f16(C::BM, C::BN, p.fmt, true);
+      int s = 0;
+      uint32_t ph = 0;
+      int as = 0;
+      uint32_t aph = 0;
+      uint32_t e_cols = 0;  // tmem column base of the metadata tile in use
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        ok = mbar_wait(bar_acce + 8 * as, aph ^ 1, err, p.status, 3);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + as * C::BN;
+        for (int kt = 0; kt < k_iters; ++kt) {
+          ok = mbar_wait(bar_full + 8 * s, ph, err, p.status, 2);
+          if (!ok) break;
+          tc_fence_after();
+          const bool new_e = (C::BK == 128) || ((kt & 1) == 0);
+          if (new_e) {
+            e_cols = C::ACC_STAGES * C::BN + 4 * s;
+            const uint64_t edesc =
+                make_smem_desc(sbase + C::OFF_E + s * C::E_BYTES, 0, 128, kSwNone);
+            tc_cp_128x128b(tmem_base + e_cols, edesc);
+          }
+          const uint32_t a_addr = sbase + C::OFF_A + s * C::A_BYTES;
+          const uint32_t b_addr = sbase + C::OFF_B + s * C::B_BYTES;
+#pragma unroll
+          for (int kb = 0; kb < C::MMAS_PER_STAGE; ++kb) {
+            const uint64_t adesc = (C::BK == 64)
+                                       ? make_smem_desc(a_addr + kb * 32, 16, 512, kSw64)
+                                       : make_smem_desc(a_addr + kb * 32, 16, 1024, kSw128);
+            const uint64_t bdesc = make_smem_desc(
+                b_addr + (kb >> 1) * C::B_SUB_BYTES + (kb & 1) * 64, 16, 1024, kSw128);
+            const int ecol = (C::BK == 128) ? kb : ((kt & 1) * 2 + kb);
+            tc_mma_sp_f16(d_tmem, adesc, bdesc, tmem_base + e_cols + (ecol & ~1),
+                          idesc | (ecol & 1), (kt > 0 || kb > 0) ? 1u : 0u);
+          }
+          tc_commit(bar_empty + 8 * s);
+          if (++s == C::STAGES) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(bar_accf + 8 * as);
+        if (++as == C::ACC_STAGES) { as = 0; aph ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                       // tensor-memory lane quadrant of this warp
+    const bool store_thread = (threadIdx.x == 64);
+    int as = 0;
+    uint32_t aph = 0;
+    uint32_t chunk_ctr = 0;
+    bool ok = true;
+    uint32_t r[32];
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m_blk = tile / p.num_n_blks;
+      const int n_blk = tile % p.num_n_blks;
+      ok = mbar_wait(bar_accf + 8 * as, aph, err, p.status, 4);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * C::BN;
+      const int tok_base = n_blk * C::BN;
+      int n_chunks = C::BN / 32;
+      {
+        const int rem = p.m_tok - tok_base;
+        const int need = (rem + 31) / 32;
+        if (need < n_chunks) n_chunks = need;
+      }
+      float bias_v = 0.f;
+      if (C::EPI == kEpiStore && p.bias != nullptr) {
+        const int o = m_blk * C::BM + q * 32 + lane;
+        if (o < p.n_out) bias_v = from_bits16(static_cast<const uint16_t*>(p.bias)[o], p.fmt);
+      }
+      for (int c = 0; c < n_chunks; ++c) {
+        tmem_ld_32x32(t_acc + c * 32, r);
+        tmem_ld_wait();
+        if (c == n_chunks - 1) {
+          // accumulator fully read: hand it back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_acce + 8 * as);
+        }
+        const uint32_t db = chunk_ctr & 1;
+        ++chunk_ctr;
+        uint8_t* stage = smem + C::OFF_D + db * C::D_BYTES;
+        if (store_thread) tma_store_wait_read<1>();
+        named_bar_sync(1, 128);
+        if (C::EPI == kEpiStore) {
+          uint16_t* srow = reinterpret_cast<uint16_t*>(stage) + q * 32 + lane;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float v = __uint_as_float(r[j]) + bias_v;
+            v = apply_act(v, p.act);
+            srow[j * C::D_COLS] = to_bits16(v, p.fmt);
+          }
+        } else {
+          // rows come in blocks of 16 gate rows then the 16 matching up rows: lanes 0..15 hold
+          // gate(f), lanes 16..31 hold up(f).  Per token pair, the lower half-warp produces token
+          // j, the upper half-warp token j+1.
+          const bool upper = lane >= 16;
+          uint16_t* scol = reinterpret_cast<uint16_t*>(stage) + q * 16 + (lane & 15);
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const uint32_t send = upper ? r[j] : r[j + 1];
+            const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 16);
+            const float g = __uint_as_float(upper ? recv : r[j]);
+            const float u = __uint_as_float(upper ? r[j + 1] : recv);
+            const float sgm = __fdividef(1.f, 1.f + __expf(-g));
+            const float h = (g * sgm) * u;
+            scol[(j + (upper ? 1 : 0)) * C::D_COLS] = to_bits16(h, p.fmt);
+          }
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(1, 128);
+        if (store_thread) {
+          tma_store_2d(&tmD, smem_u32(stage), m_blk * C::D_COLS, tok_base + c * 32);
+          tma_store_commit();
+        }
+      }
+      if (++as == C::ACC_STAGES) { as = 0; aph ^= 1; }
+    }
+    if (store_thread) tma_store_wait_all<0>();
+  }
+
+  // ------------------------------------------------------------ teardown
+  __syncwarp();
+  if (*err) {
+    // give copies that may still be in flight time to land before shared memory is released
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 1000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(p);
+  return fn;
+}
+
+// 2-D row-major tensor of 16-bit elements: [rows, cols], box [box_rows, box_cols].
+bool make_map_2d(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
+                 uint32_t box_rows, uint32_t box_cols, CUtensorMapSwizzle sw, int fmt) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstr[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                  const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <class C>
+int launch_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
+  static bool attr_set[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 16 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(sparse_gemm_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             C::SMEM_BYTES) != cudaSuccess)
+      return kErrCuda;
+    attr_set[dev] = true;
+  }
+  CUtensorMap tmA, tmB, tmD;
+  const uint64_t kc = static_cast<uint64_t>(a.K) / 2;
+  if (!make_map_2d(&tmA, a.values, a.n_out, kc, kc * 2, C::BM, C::BK / 2,
+                   C::BK == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, a.fmt))
+    return kErrTensorMap;
+  if (!make_map_2d(&tmB, a.x, a.m_tok, a.K, static_cast<uint64_t>(a.ldx) * 2, C::BN, 64,
+                   CU_TENSOR_MAP_SWIZZLE_128B, a.fmt))
+    return kErrTensorMap;
+  const int out_cols = (C::EPI == kEpiSwiGLU) ? a.n_out / 2 : a.n_out;
+  if (!make_map_2d(&tmD, a.y, a.m_tok, out_cols, static_cast<uint64_t>(a.ldy) * 2, C::D_ROWS,
+                   C::D_COLS, CU_TENSOR_MAP_SWIZZLE_NONE, a.fmt))
+    return kErrTensorMap;
+  GemmParams p;
+  p.meta = static_cast<const uint32_t*>(a.meta);
+  p.bias = a.bias;
+  p.status = a.status;
+  p.n_out = a.n_out;
+  p.m_tok = a.m_tok;
+  p.K = a.K;
+  p.k_tiles128 = (a.K + 127) / 128;
+  p.num_m_blks = (a.n_out + C::BM - 1) / C::BM;
+  p.num_n_blks = (a.m_tok + C::BN - 1) / C::BN;
+  p.fmt = a.fmt;
+  p.act = a.act;
+  const int tiles = p.num_m_blks * p.num_n_blks;
+  int grid = a.num_sms < tiles ? a.num_sms : tiles;
+  if (grid < 1) grid = 1;
+  sparse_gemm_kernel<C><<<grid, 192, C::SMEM_BYTES, stream>>>(tmA, tmB, tmD, p);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
+}
+
+template <int EPI>
+int dispatch_bn(const SparseGemmArgs& a, cudaStream_t stream) {
+  int bn = a.force_bn;
+  if (bn == 0) {
+    if (a.m_tok <= 32) bn = 32;
+    else if (a.m_tok <= 64) bn = 64;
+    else if (a.m_tok <= 128) bn = 128;
+    else if (a.m_tok <= 1024) bn = 128;
+    else bn = 256;
+  }
+  switch (bn) {
+    case 32: return launch_cfg<Cfg<32, 64, 8, EPI>>(a, stream);
+    case 64: return launch_cfg<Cfg<64, 64, 8, EPI>>(a, stream);
+    case 128: return launch_cfg<Cfg<128, 64, 8, EPI>>(a, stream);
+    case 192: return launch_cfg<Cfg<192, 64, 6, EPI>>(a, stream);
+    case 256: return launch_cfg<Cfg<256, 64, 4, EPI>>(a, stream);
+    default: return kErrInvalid;
+  }
+}
+
+}  // namespace
+
+int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream) {
+  if (a.K % 64 != 0 || a.K <= 0 || a.m_tok <= 0 || a.n_out <= 0) return kErrInvalid;
+  if (a.n_out % 8 != 0 || a.ldx % 8 != 0 || a.ldy % 8 != 0) return kErrInvalid;
+  if ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.values) |
+       reinterpret_cast<uintptr_t>(a.meta) | reinterpret_cast<uintptr_t>(a.y)) & 15)
+    return kErrInvalid;
+  if (a.epi == kEpiSwiGLU) {
+    if (a.n_out % 32 != 0 || (a.n_out / 2) % 8 != 0) return kErrInvalid;
+    return dispatch_bn<kEpiSwiGLU>(a, stream);
+  }
+  return dispatch_bn<kEpiStore>(a, stream);
+}
+
+}  // namespace sfb200
