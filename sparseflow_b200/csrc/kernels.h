@@ -66,6 +66,10 @@ struct SparseGemmArgs {
   int force_bn;           // 0 = choose by token count
 };
 int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream);
+// CTA-pair (cta_group::2) variant, 256-row x 256-token tiles; chosen by launch_sparse_gemm for
+// m_tok >= kPairMinTokens.  force_bn 1256 / 1128 selects its token tile explicitly.
+int launch_sparse_gemm_pair(const SparseGemmArgs& a, cudaStream_t stream);
+constexpr int kPairMinTokens = 1024;
 
 // ---- small-M (decode) sparse GEMM ----------------------------------------------------------
 int launch_sparse_gemm_small_m(const SparseGemmArgs& a, cudaStream_t stream);

@@ -22,6 +22,7 @@
 
 #include "kernels.h"
 #include "sm100_ptx.cuh"
+#include "tensor_map.h"
 
 namespace sfb200 {
 
@@ -310,38 +311,6 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn) return fn;
-  void* p = nullptr;
-  cudaDriverEntryPointQueryResult qres;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
-      qres != cudaDriverEntryPointSuccess)
-    return nullptr;
-  fn = reinterpret_cast<EncodeTiledFn>(p);
-  return fn;
-}
-
-// 2-D row-major tensor of 16-bit elements: [rows, cols], box [box_rows, box_cols].
-bool make_map_2d(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes,
-                 uint32_t box_rows, uint32_t box_cols, CUtensorMapSwizzle sw, int fmt) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (!fn) return false;
-  cuuint64_t gdim[2] = {cols, rows};
-  cuuint64_t gstr[1] = {pitch_bytes};
-  cuuint32_t box[2] = {box_cols, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(m, fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
-                  const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
-}
-
 template <class C>
 int launch_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
   static bool attr_set[16] = {};
@@ -412,6 +381,9 @@ int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream) {
   if ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.values) |
        reinterpret_cast<uintptr_t>(a.meta) | reinterpret_cast<uintptr_t>(a.y)) & 15)
     return kErrInvalid;
+  // CTA-pair kernel for prefill-sized token counts (or when forced: 1256 / 1128)
+  if (a.force_bn >= 1000 || (a.force_bn == 0 && a.m_tok >= kPairMinTokens))
+    return launch_sparse_gemm_pair(a, stream);
   if (a.epi == kEpiSwiGLU) {
     if (a.n_out % 32 != 0 || (a.n_out / 2) % 8 != 0) return kErrInvalid;
     return dispatch_bn<kEpiSwiGLU>(a, stream);
