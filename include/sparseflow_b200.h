@@ -148,6 +148,11 @@ SFB200_API int sfb200_ffn_forward(const sfb200_ffn_weights* w, const void* x, in
 SFB200_API int sfb200_ffn_forward_host(const sfb200_ffn_weights* w, const void* x_host,
                                        void* out_host, int M, void* stream);
 
+/* Tuning hook: force the token tile of the tcgen05 kernels on the current device.  0 = automatic;
+ * 32/64/128/192/256 = single-CTA kernel with that tile; 1128/1256 = CTA-pair kernel with a
+ * 128/256-token tile.  No counterpart upstream. */
+SFB200_API int sfb200_debug_force_token_tile(int bn);
+
 /* ------------------------------------------------------------------ 2. sf_* runtime API --- */
 /* experiments/old_structure/runtime/api/sparseflow_api.h:8-28, exercised by tests/test_c_api.cpp. */
 

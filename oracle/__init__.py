@@ -14,6 +14,7 @@ from .sparse24 import (  # noqa: F401
     PAIR_TO_REF_CODE,
     prune_24,
     prune_24_loop,
+    prune_24_pruned_chunked,
     hw_nibbles,
     hw_meta_tiled,
     hw_meta_tiled_to_nibbles,

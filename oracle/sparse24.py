@@ -120,6 +120,16 @@ def prune_24(bits: np.ndarray, dtype: str = "f16", tie: str = "high") -> dict:
     return dict(pruned=pruned, values=values, idx0=idx0, idx1=idx1, ref_codes=ref_codes)
 
 
+def prune_24_pruned_chunked(bits: np.ndarray, dtype: str = "f16", tie: str = "high",
+                             chunk_rows: int = 2048) -> np.ndarray:
+    """Pruned-dense matrix only, computed in row chunks to bound memory on large weights."""
+    bits = np.ascontiguousarray(bits, dtype=np.uint16)
+    out = np.empty_like(bits)
+    for r0 in range(0, bits.shape[0], chunk_rows):
+        out[r0:r0 + chunk_rows] = prune_24(bits[r0:r0 + chunk_rows], dtype, tie)["pruned"]
+    return out
+
+
 def prune_24_loop(bits: np.ndarray, dtype: str = "f16") -> dict:
     """Literal loop form of experiments/prune_24_cpu.py:17-28 (small inputs only).
 

@@ -1,0 +1,161 @@
+"""Host-side checks of the C-ABI library: it loads, exports every symbol the header declares, keeps
+the reference's sf_* selection semantics (tests/test_c_api.cpp) and the C ABI v1 error behaviour
+(tests/abi/test_abi_stability.c).  No compute call is made, so no GPU is needed."""
+import ctypes as C
+import os
+import re
+import sqlite3
+import subprocess
+
+import pytest
+
+from sparseflow_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    hdr = open(os.path.join(ROOT, "include", "sparseflow_b200.h")).read()
+    hdr = hdr.replace('#define SFB200_API __attribute__((visibility("default")))', "")
+    declared = set(re.findall(r"SFB200_API[^;(]*?\b(\w+)\s*\(", hdr))
+    assert len(declared) >= 35
+    out = subprocess.check_output(["nm", "-D", "--defined-only", _lib.LIB_PATH]).decode()
+    exported = {line.split()[-1] for line in out.splitlines() if line.strip()}
+    assert declared <= exported, sorted(declared - exported)
+
+
+def test_sizes_and_strings(lib):
+    assert lib.sfb200_values_bytes(128, 128) == 128 * 64 * 2
+    assert lib.sfb200_meta_bytes(128, 128) == 2048
+    assert lib.sfb200_meta_bytes(129, 130) == 4 * 2048
+    assert lib.sfb200_meta_bytes(22016, 4096) == 172 * 32 * 2048
+    assert b"invalid" in lib.sfb200_status_string(1)
+    assert lib.sfb200_version() >= 100
+
+
+def _desc(M=512, N=512, K=512, dtype=0, sp=0, ratio=0.0):
+    return _lib.MatmulDesc(M, N, K, dtype, sp, ratio, 0)
+
+
+def _sf(lib):
+    lib.sf_select_kernel.restype = C.c_int32
+    lib.sf_select_kernel.argtypes = [C.c_char_p, C.POINTER(_lib.MatmulDesc), C.POINTER(_lib.GpuInfo)]
+    lib.sf_cache_size.restype = C.c_int32
+    lib.sf_cache_size.argtypes = [C.c_char_p]
+    lib.sf_cache_clear.argtypes = [C.c_char_p]
+    lib.sf_bucket_dimension.restype = C.c_int32
+    lib.sf_bucket_dimension.argtypes = [C.c_int32]
+    lib.sf_note_compressed.argtypes = [C.c_char_p, C.POINTER(_lib.MatmulDesc)]
+    lib.sf_record_sparse_failure.argtypes = [C.c_char_p, C.POINTER(_lib.MatmulDesc), C.POINTER(_lib.GpuInfo)]
+    return lib
+
+
+def test_sf_api_follows_reference_test_c_api(lib, tmp_path):
+    """The sequence of tests/test_c_api.cpp: dense-typed desc, repeat, then M=513 (next bucket)."""
+    sf = _sf(lib)
+    db = str(tmp_path / "test_c_api.db").encode()
+    sf.sf_cache_clear(db)
+    d = _desc()
+    g = _lib.GpuInfo(86, 82, 100)
+    k1 = sf.sf_select_kernel(db, C.byref(d), C.byref(g))
+    assert k1 == 0                                   # dense-typed desc is cached as dense
+    assert sf.sf_cache_size(db) == 1
+    k2 = sf.sf_select_kernel(db, C.byref(d), C.byref(g))
+    assert k2 == k1 and sf.sf_cache_size(db) == 1    # cache hit, no new row
+    d.M = 513
+    sf.sf_select_kernel(db, C.byref(d), C.byref(g))
+    assert sf.sf_cache_size(db) == 2                 # 513 buckets to 1024: a second row
+    # the table is the reference's schema and key format
+    con = sqlite3.connect(db.decode())
+    rows = dict(con.execute("SELECT key_hash, best_kernel FROM kernel_cache").fetchall())
+    assert "M=512;N=512;K=512;dtype=0;layout=0;sp=0;sm=86" in rows
+    assert "M=1024;N=512;K=512;dtype=0;layout=0;sp=0;sm=86" in rows
+    cols = [r[1] for r in con.execute("PRAGMA table_info(kernel_cache)")]
+    assert cols == ["key_hash", "best_kernel", "best_gflops", "sparse_failed", "failure_count",
+                    "last_failure_code", "last_failure_ts"]
+    con.close()
+    sf.sf_cache_clear(db)
+    assert sf.sf_cache_size(db) == 0
+
+
+def test_sf_bucketing(lib):
+    sf = _sf(lib)
+    assert [sf.sf_bucket_dimension(v) for v in (0, 1, 32, 33, 512, 513, 2048, 40000, 70000)] == \
+        [0, 32, 32, 64, 512, 1024, 2048, 65535, 65535]
+
+
+def test_sf_eligibility_rules_without_gpu(lib, tmp_path):
+    sf = _sf(lib)
+    db = str(tmp_path / "elig.db").encode()
+    g = _lib.GpuInfo(100, 148, 227)
+    small = _desc(64, 64, 64, 1, 1, 0.5)             # 2:4 but under 512^3 flops -> dense, cached
+    assert sf.sf_select_kernel(db, C.byref(small), C.byref(g)) == 0
+    assert sf.sf_cache_size(db) == 1
+    big = _desc(4096, 4096, 4096, 1, 1, 0.5)         # eligible size, compression not cached -> dense, cached
+    assert sf.sf_select_kernel(db, C.byref(big), C.byref(g)) == 0
+    assert sf.sf_cache_size(db) == 2
+    # quarantine bookkeeping lands in the table
+    other = _desc(8192, 4096, 4096, 1, 1, 0.5)
+    for _ in range(3):
+        sf.sf_record_sparse_failure(db, C.byref(other), C.byref(g))
+    con = sqlite3.connect(db.decode())
+    row = con.execute("SELECT sparse_failed, failure_count FROM kernel_cache WHERE key_hash LIKE 'M=8192;%'").fetchone()
+    con.close()
+    assert row == (1, 3)
+
+
+def test_sf_null_path_uses_default_name(lib, tmp_path, monkeypatch):
+    sf = _sf(lib)
+    monkeypatch.chdir(tmp_path)
+    d, g = _desc(), _lib.GpuInfo(100, 148, 227)
+    sf.sf_select_kernel(None, C.byref(d), C.byref(g))
+    assert os.path.exists(tmp_path / "kernel_cache.db")
+    assert sf.sf_cache_size(None) == 1
+
+
+class _Version(C.Structure):
+    _fields_ = [("major", C.c_int), ("minor", C.c_int), ("patch", C.c_int)]
+
+
+def test_abi_v1_host_behaviour(lib):
+    """tests/abi/test_abi_stability.c: version/compat, NULL ctx -> INVALID_ARGUMENT, strings."""
+    lib.sparseflow_get_version.restype = _Version
+    v = lib.sparseflow_get_version()
+    assert (v.major, v.minor) == (1, 1)
+    assert lib.sparseflow_is_abi_compatible(1, 0) == 1
+    assert lib.sparseflow_is_abi_compatible(1, 7) == 1
+    assert lib.sparseflow_is_abi_compatible(2, 0) == 0
+    lib.sparseflow_get_error_string.restype = C.c_char_p
+    lib.sparseflow_get_last_error.restype = C.c_char_p
+    assert lib.sparseflow_get_error_string(0) == b"Success"
+    assert lib.sparseflow_get_error_string(5) == b"Invalid handle"
+    assert lib.sparseflow_create_context(None, 0) == 1            # NULL out-pointer
+    assert b"NULL" in lib.sparseflow_get_last_error()
+    assert lib.sparseflow_destroy_context(None) == 5              # NULL handle
+    assert lib.sparseflow_destroy_kernel(None) == 5
+    is_valid = C.c_int(-1)
+    assert lib.sparseflow_validate_2_4(None, 4, 4, 0, C.byref(is_valid)) == 1
+    assert lib.sparseflow_sparse_gemm(None, None, None, None, 1, 1, 1, 0, None) == 5
+    lib.sparseflow_compressed_meta_offset.restype = C.c_size_t
+    assert lib.sparseflow_compressed_meta_offset(128, 128) == 16384
+    assert lib.sparseflow_compressed_meta_offset(8, 72) % 256 == 0
+
+
+def test_compute_calls_fail_loudly_without_a_device(lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    rc = lib.sfb200_prune_compress_24(None, 4, 16, 16, 0, 0, None, None, None, None, None)
+    assert rc == 3                                             # SFB200_ERROR_CUDA, not a silent fallback
+    ctx = C.c_void_p()
+    assert lib.sparseflow_create_context(C.byref(ctx), 0) == 3
+
+
+def test_package_has_no_oracle_dependency():
+    """The product path must not import the oracle."""
+    pkg = os.path.join(ROOT, "sparseflow_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cpp", ".h", ".cuh")):
+                src = open(os.path.join(dirpath, f)).read()
+                assert not re.search(r"^\s*(import|from)\s+oracle\b", src, re.M), f

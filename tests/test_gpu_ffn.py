@@ -1,0 +1,185 @@
+"""Gated FFN and the nn modules on the GPU against the oracle."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+import oracle as o
+from sparseflow_b200 import _lib, ops
+from sparseflow_b200.fused_mlp import SparseFlowFusedMLP
+from sparseflow_b200.kernels.fused_silu_mul import fused_silu_mul
+from sparseflow_b200.nn.policy import SparseFlowPolicy
+from sparseflow_b200.nn.sparseflow_linear import SparseFlowLinear, make_sparseflow_linear
+from sparseflow_b200.nn.sparseflow_mlp import SparseFlowMLP, make_sparseflow_mlp
+from tests.util import bits_of, seeded_act, seeded_weight, to_dev
+
+pytestmark = pytest.mark.gpu
+REL_TOL = 1e-2
+
+
+@pytest.fixture(autouse=True)
+def _auto_tile():
+    ops.force_token_tile(0)
+    yield
+    ops.force_token_tile(0)
+
+
+def _weights(H, I, dt):
+    wg, wu, wd = seeded_weight(I, H, dt, 1), seeded_weight(I, H, dt, 2), seeded_weight(H, I, dt, 3)
+    return wg, wu, wd, [o.prune_24(w, dt)["pruned"] for w in (wg, wu, wd)]
+
+
+@pytest.mark.parametrize("bn", [0, 64, 192, 1128, 1256])
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+def test_swiglu_epilogue(bn, dt):
+    H, I, M = 512, 352, 300
+    wg, wu, _, (pg, pu, _) = _weights(H, I, dt)
+    x = seeded_act(M, H, dt, 1234)
+    cw = ops.compress_gate_up(to_dev(wg, dt), to_dev(wu, dt))
+    ops.force_token_tile(bn)
+    h = ops.sparse_gemm_swiglu(to_dev(x, dt), cw)
+    assert ops.device_status() == 0
+    ref = o.silu_mul_ref(o.gemm_ref(x, pg, dt), o.gemm_ref(x, pu, dt))
+    assert o.rel_err_metrics(o.to_f32(bits_of(h), dt), ref)["floor"] <= REL_TOL
+
+
+@pytest.mark.parametrize("H,I,M", [(512, 1408, 100), (4096, 11008, 512)])
+def test_ffn_forward_c_abi_device_and_host(H, I, M):
+    """sfb200_ffn_forward / sfb200_ffn_forward_host against the oracle; (4096, 11008, 512) is the
+    Llama-7B shape at its smallest token count."""
+    dt = "bf16"
+    wg, wu, wd, (pg, pu, pd) = _weights(H, I, dt)
+    x = seeded_act(M, H, dt, 1235)
+    gu = ops.compress_gate_up(to_dev(wg, dt), to_dev(wu, dt))
+    dn = ops.compress_weight(to_dev(wd, dt))
+    W = _lib.FFNWeights(H, I, ops.BF16, gu.values.data_ptr(), gu.meta.data_ptr(), dn.values.data_ptr(),
+                        dn.meta.data_ptr(), None)
+    xd = to_dev(x, dt)
+    hidden = torch.empty(M, I, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(M, H, device="cuda", dtype=torch.bfloat16)
+    L = _lib.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    assert L.sfb200_ffn_forward(C.byref(W), xd.data_ptr(), H, hidden.data_ptr(), out.data_ptr(), H, M, st) == 0
+    assert ops.device_status() == 0
+    fused = o.ffn_ref(x, pg, pu, pd, dt, round_gate_up=False)     # the dataflow the kernels implement
+    unfused = o.ffn_ref(x, pg, pu, pd, dt, round_gate_up=True)    # the reference's unfused dataflow
+    y = o.to_f32(bits_of(out), dt)
+    mh = o.rel_err_metrics(o.to_f32(bits_of(hidden), dt), o.to_f32(fused["hidden"], dt))
+    mf = o.rel_err_metrics(y, fused["out_f32"])
+    mu = o.rel_err_metrics(y, unfused["out_f32"])
+    assert mh["floor"] <= REL_TOL, mh
+    assert mf["floor"] <= REL_TOL, mf
+    assert mu["norm"] <= REL_TOL, mu          # extra rounding of gate/up shows only as noise
+    # host-buffer entry point: same bits as the device path
+    xh = torch.from_numpy(x.view(np.int16)).pin_memory()
+    oh = torch.empty(M, H, dtype=torch.int16).pin_memory()
+    assert L.sfb200_ffn_forward_host(C.byref(W), xh.data_ptr(), oh.data_ptr(), M, st) == 0
+    assert (oh.numpy().view(np.uint16) == bits_of(out)).all()
+
+
+def test_fused_silu_mul_kernel():
+    dt = "f16"
+    g, u = seeded_act(300, 1000, dt, 1), seeded_act(300, 1000, dt, 2)
+    gu = torch.cat([to_dev(g, dt), to_dev(u, dt)], 1)                  # strided rows, like chunk(2)
+    out = fused_silu_mul(*gu.chunk(2, dim=-1))
+    ref = o.silu_mul_ref(o.to_f32(g, dt), o.to_f32(u, dt))
+    assert o.rel_err_metrics(o.to_f32(bits_of(out), dt), ref)["floor"] <= 2e-3
+    odd = fused_silu_mul(to_dev(g, dt)[:, :999], to_dev(u, dt)[:, :999])  # scalar path
+    assert o.rel_err_metrics(o.to_f32(bits_of(odd), dt), ref[:, :999])["floor"] <= 2e-3
+
+
+def _linears(H, I, dt, prune):
+    tdt = torch.bfloat16 if dt == "bf16" else torch.float16
+    wg, wu, wd, pr = _weights(H, I, dt)
+    src = pr if prune else (wg, wu, wd)
+    mods = []
+    for w, (o_f, i_f) in zip(src, [(I, H), (I, H), (H, I)]):
+        lin = nn.Linear(i_f, o_f, bias=False, device="cuda", dtype=tdt)
+        lin.weight.data.copy_(to_dev(w, dt))
+        mods.append(lin)
+    return mods, pr
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+def test_fused_mlp_module_force_modes(dt):
+    H, I, M = 512, 1408, 320
+    (gp, up, dp), (pg, pu, pd) = _linears(H, I, dt, prune=True)
+    x = seeded_act(M, H, dt, 99)
+    ref = o.ffn_ref(x, pg, pu, pd, dt, round_gate_up=False)["out_f32"]
+    xs = to_dev(x, dt).view(4, 80, H)
+    for mode in ("sparse", "dense", "auto"):
+        mlp = SparseFlowFusedMLP(gp, up, dp, force_mode=mode)
+        assert mlp._gate_up_sparse is not None and mlp._down_sparse is not None
+        y = mlp(xs)
+        assert y.shape == (4, 80, H)
+        m = o.rel_err_metrics(o.to_f32(bits_of(y), dt).reshape(M, H), ref)
+        assert m["norm"] <= REL_TOL, (mode, m)          # reference smoke bound is 0.5 abs (tools/smoke_dispatch.py:83)
+    assert ops.device_status() == 0
+    # a weight that is not 2:4 leaves the module dense, as upstream
+    (gd, ud, dd), _ = _linears(H, I, dt, prune=False)
+    dense_mlp = SparseFlowFusedMLP(gd, ud, dd)
+    assert dense_mlp._gate_up_sparse is None and dense_mlp._down_sparse is None
+    dense_mlp(xs)
+    with pytest.raises(RuntimeError):
+        SparseFlowFusedMLP(gd, ud, dd, force_mode="sparse")(xs)
+
+
+def test_sparseflow_linear_module():
+    dt = "bf16"
+    w = seeded_weight(1024, 512, dt, 4)
+    b = seeded_act(1, 1024, dt, 8)[0]
+    pol = SparseFlowPolicy(min_M_default=64)
+    lin = SparseFlowLinear(to_dev(w, dt), to_dev(b, dt), policy=pol, op_name="default", dense_uses_pruned=True)
+    x = seeded_act(200, 512, dt, 5)
+    y = lin(to_dev(x, dt).view(2, 100, 512))
+    assert lin._sparse_count == 1 and y.shape == (2, 100, 1024)
+    ref = o.gemm_ref(x, o.prune_24(w, dt)["pruned"], dt) + o.to_f32(b, dt)[None]
+    assert o.rel_err_metrics(o.to_f32(bits_of(y), dt).reshape(200, 1024), ref)["floor"] <= REL_TOL
+    y_small = lin(to_dev(x, dt)[:8])                         # below min_M: dense branch, pruned weight
+    assert lin._dense_count == 1
+    assert o.rel_err_metrics(o.to_f32(bits_of(y_small), dt), ref[:8])["floor"] <= REL_TOL
+    assert (bits_of(lin.W_dense_pruned) == o.prune_24(w, dt)["pruned"]).all()
+    sd = lin.state_dict()
+    assert set(sd) == {"W_original", "W_dense_pruned", "bias"}
+    m = make_sparseflow_linear(nn.Linear(512, 64, device="cuda", dtype=torch.float16), name="q_proj")
+    assert m.op_name == "q_proj"
+    with pytest.raises(ValueError):
+        lin(torch.zeros(2, 100, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(TypeError):
+        make_sparseflow_linear(nn.ReLU())
+
+
+def test_sparseflow_mlp_module():
+    dt = "f16"
+    H, I = 512, 704
+    wg, wu, wd, (pg, pu, pd) = _weights(H, I, dt)
+    x = seeded_act(96, H, dt, 6)
+    xs = to_dev(x, dt).view(2, 48, H)
+    mlp = SparseFlowMLP(H, I, to_dev(wg, dt), to_dev(wu, dt), to_dev(wd, dt))
+    y = mlp(xs)
+    # reference function: sparse gate/up on pruned weights, DENSE down on the unpruned weight
+    hid = o.from_f32(o.silu_mul_ref(o.gemm_ref(x, pg, dt), o.gemm_ref(x, pu, dt)), dt)
+    ref = o.to_f32(hid, dt) @ o.to_f32(wd, dt).T
+    assert o.rel_err_metrics(o.to_f32(bits_of(y), dt).reshape(96, H), ref)["floor"] <= REL_TOL
+    mlp_s = SparseFlowMLP(H, I, to_dev(wg, dt), to_dev(wu, dt), to_dev(wd, dt), down_mode="sparse")
+    ref_s = o.ffn_ref(x, pg, pu, pd, dt, round_gate_up=False)["out_f32"]
+    assert o.rel_err_metrics(o.to_f32(bits_of(mlp_s(xs)), dt).reshape(96, H), ref_s)["floor"] <= REL_TOL
+    # biases on gate/up take the unfused path
+    bg, bu = seeded_act(1, I, dt, 11)[0], seeded_act(1, I, dt, 12)[0]
+    mlp_b = SparseFlowMLP(H, I, to_dev(wg, dt), to_dev(wu, dt), to_dev(wd, dt), to_dev(bg, dt), to_dev(bu, dt),
+                          down_mode="sparse")
+    g = o.to_f32(o.from_f32(o.gemm_ref(x, pg, dt) + o.to_f32(bg, dt)[None], dt), dt)
+    u = o.to_f32(o.from_f32(o.gemm_ref(x, pu, dt) + o.to_f32(bu, dt)[None], dt), dt)
+    ref_b = o.gemm_ref(o.from_f32(o.silu_mul_ref(g, u), dt), pd, dt)
+    assert o.rel_err_metrics(o.to_f32(bits_of(mlp_b(xs)), dt).reshape(96, H), ref_b)["norm"] <= REL_TOL
+
+    class Gated(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.gate_proj = nn.Linear(H, I, bias=False, device="cuda", dtype=torch.float16)
+            self.up_proj = nn.Linear(H, I, bias=False, device="cuda", dtype=torch.float16)
+            self.down_proj = nn.Linear(I, H, bias=False, device="cuda", dtype=torch.float16)
+    assert isinstance(make_sparseflow_mlp(Gated()), SparseFlowMLP)
+    assert ops.device_status() == 0
