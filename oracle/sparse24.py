@@ -311,8 +311,11 @@ def interleave_gate_up_rows(I: int, block: int = 16) -> np.ndarray:
 
 
 def rel_err_metrics(y: np.ndarray, y_ref: np.ndarray) -> dict:
-    """The three relative-error definitions in use for this path:
-      floor: |d| / max(|ref|, 1e-2 * rms(ref))   (the bound tests assert on)
+    """Relative-error definitions in use for this path:
+      floor: |d| / max(|ref|, 1e-2 * rms(ref))   single GEMM / epilogue: the bound tests assert on
+      chain: |d| / max(|ref|, rms(ref))          gated-FFN output: an element far below the rms is a
+             cancellation of ~I/2 products whose 16-bit hidden inputs each carry 2^-9 relative
+             rounding, so its error scale is the rms, not its own magnitude
       eps:   |d| / (|ref| + 1e-6)                (tests/test_sparse_pytest.py:44)
       norm:  max|d| / max|ref|                   (demo/demo_harness.py:187)
     """
@@ -324,6 +327,7 @@ def rel_err_metrics(y: np.ndarray, y_ref: np.ndarray) -> dict:
     return dict(
         max_abs=float(d.max()) if d.size else 0.0,
         floor=float((d / floor).max()) if d.size else 0.0,
+        chain=float((d / np.maximum(np.abs(r), rms + 1e-30)).max()) if d.size else 0.0,
         eps=float((d / (np.abs(r) + 1e-6)).max()) if d.size else 0.0,
         norm=float(d.max() / max(np.abs(r).max(), 1e-30)) if d.size else 0.0,
     )

@@ -67,11 +67,13 @@ def test_ffn_forward_c_abi_device_and_host(H, I, M):
     unfused = o.ffn_ref(x, pg, pu, pd, dt, round_gate_up=True)    # the reference's unfused dataflow
     y = o.to_f32(bits_of(out), dt)
     mh = o.rel_err_metrics(o.to_f32(bits_of(hidden), dt), o.to_f32(fused["hidden"], dt))
+    md = o.rel_err_metrics(y, o.gemm_ref(bits_of(hidden), pd, dt))     # down GEMM alone, same input bits
     mf = o.rel_err_metrics(y, fused["out_f32"])
     mu = o.rel_err_metrics(y, unfused["out_f32"])
     assert mh["floor"] <= REL_TOL, mh
-    assert mf["floor"] <= REL_TOL, mf
-    assert mu["norm"] <= REL_TOL, mu          # extra rounding of gate/up shows only as noise
+    assert md["floor"] <= REL_TOL, md
+    assert mf["chain"] <= REL_TOL and mf["norm"] <= REL_TOL, mf
+    assert mu["chain"] <= REL_TOL and mu["norm"] <= REL_TOL, mu   # extra rounding of gate/up shows only as noise
     # host-buffer entry point: same bits as the device path
     xh = torch.from_numpy(x.view(np.int16)).pin_memory()
     oh = torch.empty(M, H, dtype=torch.int16).pin_memory()
@@ -115,7 +117,7 @@ def test_fused_mlp_module_force_modes(dt):
         y = mlp(xs)
         assert y.shape == (4, 80, H)
         m = o.rel_err_metrics(o.to_f32(bits_of(y), dt).reshape(M, H), ref)
-        assert m["norm"] <= REL_TOL, (mode, m)          # reference smoke bound is 0.5 abs (tools/smoke_dispatch.py:83)
+        assert m["chain"] <= REL_TOL and m["norm"] <= REL_TOL, (mode, m)          # reference smoke bound is 0.5 abs (tools/smoke_dispatch.py:83)
     assert ops.device_status() == 0
     # a weight that is not 2:4 leaves the module dense, as upstream
     (gd, ud, dd), _ = _linears(H, I, dt, prune=False)
@@ -162,10 +164,10 @@ def test_sparseflow_mlp_module():
     # reference function: sparse gate/up on pruned weights, DENSE down on the unpruned weight
     hid = o.from_f32(o.silu_mul_ref(o.gemm_ref(x, pg, dt), o.gemm_ref(x, pu, dt)), dt)
     ref = o.to_f32(hid, dt) @ o.to_f32(wd, dt).T
-    assert o.rel_err_metrics(o.to_f32(bits_of(y), dt).reshape(96, H), ref)["floor"] <= REL_TOL
+    assert o.rel_err_metrics(o.to_f32(bits_of(y), dt).reshape(96, H), ref)["chain"] <= REL_TOL
     mlp_s = SparseFlowMLP(H, I, to_dev(wg, dt), to_dev(wu, dt), to_dev(wd, dt), down_mode="sparse")
     ref_s = o.ffn_ref(x, pg, pu, pd, dt, round_gate_up=False)["out_f32"]
-    assert o.rel_err_metrics(o.to_f32(bits_of(mlp_s(xs)), dt).reshape(96, H), ref_s)["floor"] <= REL_TOL
+    assert o.rel_err_metrics(o.to_f32(bits_of(mlp_s(xs)), dt).reshape(96, H), ref_s)["chain"] <= REL_TOL
     # biases on gate/up take the unfused path
     bg, bu = seeded_act(1, I, dt, 11)[0], seeded_act(1, I, dt, 12)[0]
     mlp_b = SparseFlowMLP(H, I, to_dev(wg, dt), to_dev(wu, dt), to_dev(wd, dt), to_dev(bg, dt), to_dev(bu, dt),
@@ -173,7 +175,7 @@ def test_sparseflow_mlp_module():
     g = o.to_f32(o.from_f32(o.gemm_ref(x, pg, dt) + o.to_f32(bg, dt)[None], dt), dt)
     u = o.to_f32(o.from_f32(o.gemm_ref(x, pu, dt) + o.to_f32(bu, dt)[None], dt), dt)
     ref_b = o.gemm_ref(o.from_f32(o.silu_mul_ref(g, u), dt), pd, dt)
-    assert o.rel_err_metrics(o.to_f32(bits_of(mlp_b(xs)), dt).reshape(96, H), ref_b)["norm"] <= REL_TOL
+    assert o.rel_err_metrics(o.to_f32(bits_of(mlp_b(xs)), dt).reshape(96, H), ref_b)["chain"] <= REL_TOL
 
     class Gated(nn.Module):
         def __init__(self):
