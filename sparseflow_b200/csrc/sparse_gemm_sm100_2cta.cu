@@ -1,16 +1,19 @@
 // 2:4-sparse GEMM for sm_100a, CTA-pair variant for prefill-sized token counts.
 //
 // Same math and operand formats as sparse_gemm_sm100.cu, but two CTAs (a cluster of 2, on an SM
-// pair) work on one 256-row x 256-token tile with tcgen05.mma.sp.cta_group::2:
-//   * each CTA holds 128 weight rows (its own compressed values + metadata tile) and HALF of the
-//     token tile, so per MMA an SM reads 4 KiB of A + 8 KiB of B from shared memory instead of
-//     4 + 16: this is what lifts the single-CTA kernel's shared-memory and L2 bandwidth bound
-//     (tile intensity 2RT/(R+2T) = 171 flop/B against 96-102 for 128x192/256);
+// pair) work on one tile of (256 * RS) weight rows x BN tokens with tcgen05.mma.sp.cta_group::2:
+//   * each CTA holds RS sub-tiles of 128 weight rows (compressed values + metadata) and HALF of
+//     the token tile; per k-block it issues RS MMAs (M = 256 across the pair, N = BN) that share
+//     the token operand.  What this buys is bytes: the kernel is bound by what L2 can feed the
+//     SMs, and a tile of R rows x T tokens moves R*K + 2*T*K bytes for 2*R*T*K flops, i.e.
+//     2RT/(R+2T) flop/B: 96-102 for the single-CTA 128x192/256 tiles, 171 for 256x256 (RS = 1),
+//     229 for 512x208 (RS = 2).  Shared-memory reads per MMA drop the same way (each SM reads half
+//     of the token tile);
 //   * the even CTA of the pair issues every MMA; completion is signalled to both CTAs;
-//   * the accumulator is 128 lanes x 256 fp32 columns per CTA and single-buffered (tensor memory
-//     has 512 columns and the metadata needs some), so the epilogue drains it fast: 8 warps pull
-//     their 128 columns into packed 16-bit registers, hand the accumulator back, and only then
-//     write to global memory while the next tile's main loop is already running.
+//   * accumulators (RS x BN fp32 columns, 128 lanes per CTA) are single-buffered: tensor memory
+//     has 512 columns and the metadata needs some.  The epilogue streams them out in 16-column
+//     chunks with the next chunk's tcgen05.ld in flight, and hands the accumulators back right
+//     after the last load; its stores overlap the next tile's main loop.
 //
 // 10 warps: warp 0 = TMA producer, warp 1 = MMA issuer / tensor-memory owner, warps 2..9 = epilogue.
 // All loads are plain per-CTA TMA copies; nothing here reads another GPU's memory.
@@ -43,9 +46,12 @@ __device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
   return r;
 }
+// Arrive on a barrier of the pair's even CTA.  Default semantics (release at CTA scope) on purpose:
+// a cluster-scope release would hold the arrive back until this thread's global stores of the
+// previous tile have reached L2, and the arrive only has to order tensor-memory reads, which
+// tcgen05.wait::ld + tcgen05.fence::before_thread_sync already do.
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
-               : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // Pair forms: the copy lands in this CTA's shared memory, the byte count is credited to the
 // barrier of the even CTA of the pair.
@@ -106,36 +112,52 @@ struct PairParams {
   void* y;
   int* status;
   int n_out, m_tok, K, ldy;
-  int num_m_blks, num_n_blks;   // 256-row / BN-token tiles
+  int num_m_blks, num_n_blks;   // (256*RS)-row / BN-token tiles
   int k_tiles128;
   int fmt, act;
 };
 
-template <int BN_, int BK_, int STAGES_, int EPI_>
+template <int BN_, int BK_, int STAGES_, int RS_, int EPI_>
 struct PairCfg {
   static constexpr int BN = BN_;         // tokens per tile (pair-wide)
   static constexpr int BK = BK_;
   static constexpr int STAGES = STAGES_;
+  static constexpr int RS = RS_;         // 128-row sub-tiles per CTA
   static constexpr int EPI = EPI_;
+  static constexpr int ROWS_CTA = 128 * RS;
+  static constexpr int ROWS_TILE = 2 * ROWS_CTA;
   static constexpr int HALF_N = BN / 2;  // tokens loaded by each CTA
-  static constexpr int A_BYTES = 128 * (BK / 2) * 2;
+  static constexpr int A_SUB_BYTES = 128 * (BK / 2) * 2;
+  static constexpr int A_BYTES = RS * A_SUB_BYTES;
   static constexpr int B_SUBS = BK / 64;
   static constexpr int B_SUB_BYTES = HALF_N * 128;
   static constexpr int B_BYTES = B_SUBS * B_SUB_BYTES;
-  static constexpr int E_BYTES = 2048;
+  static constexpr int E_SUB_BYTES = 2048;
+  static constexpr int E_BYTES = RS * E_SUB_BYTES;
   static constexpr int MMAS_PER_STAGE = BK / 32;
-  static constexpr int E_COL0 = BN;      // metadata columns start after the accumulator
-  static constexpr int TMEM_USED = BN + 4 * STAGES;
+  // Metadata tiles cover K = 128: with BK = 64 one tile serves two stages, so the metadata ring
+  // (shared memory and tensor-memory columns) has STAGES/2 + 1 slots.  A slot is reused
+  // STAGES + 2 stages after it was written, i.e. after the stage barrier that guards it.
+  static constexpr int E_STAGES = (BK == 128) ? STAGES : STAGES / 2 + 1;
+  static constexpr int E_COL0 = RS * BN;          // metadata columns start after the accumulators
+  static constexpr int E_COLS_STAGE = 4 * RS;
+  static constexpr int TMEM_USED = RS * BN + E_COLS_STAGE * E_STAGES;
   static constexpr int TMEM_COLS = TMEM_USED <= 128 ? 128 : TMEM_USED <= 256 ? 256 : 512;
   static constexpr int OFF_A = 0;
   static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
   static constexpr int OFF_E = OFF_B + STAGES * B_BYTES;
-  static constexpr int OFF_BAR = OFF_E + STAGES * E_BYTES;
+  static constexpr int OFF_BAR = OFF_E + E_STAGES * E_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
   static constexpr int EPI_WARPS = 8;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
-  static constexpr int COLS_PER_WARP = BN / 2;   // two warps share a lane quadrant
-  static_assert(BN % 64 == 0 && BN <= 256, "BN");
+  // 8 epilogue warps = 4 lane quadrants x 2: with RS = 1 the two warps of a quadrant split the
+  // columns, with RS = 2 each takes one accumulator.
+  static constexpr int COLS_PER_WARP = (RS == 1) ? BN / 2 : BN;
+  static_assert(RS == 1 || RS == 2, "RS");
+  static_assert(BK == 128 || STAGES % 2 == 0, "BK = 64 needs an even stage count");
+  static_assert(BN % 16 == 0 && BN <= 256, "BN");
+  static_assert(HALF_N % 8 == 0, "token half must be whole swizzle atoms");
+  static_assert(COLS_PER_WARP % 16 == 0, "epilogue chunking");
   static_assert(TMEM_USED <= 512, "tmem");
   static_assert(SMEM_BYTES <= 232448, "smem");
 };
@@ -148,18 +170,52 @@ __device__ __forceinline__ float act_fn(float v, int act) {
     default: return v;
   }
 }
-__device__ __forceinline__ uint32_t pack2(float a, float b, int fmt) {
-  if (fmt == 1) {
-    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<const uint32_t*>(&v);
-  }
-  const __half2 v = __floats2half2_rn(a, b);
-  return *reinterpret_cast<const uint32_t*>(&v);
+__device__ __forceinline__ uint16_t to16(float v, int fmt) {
+  if (fmt == 1) return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+  return __half_as_ushort(__float2half_rn(v));
 }
 __device__ __forceinline__ float bias_at(const void* bias, int o, int fmt) {
   const uint16_t b = static_cast<const uint16_t*>(bias)[o];
   if (fmt == 1) return __uint_as_float(static_cast<uint32_t>(b) << 16);
   return __half2float(__ushort_as_half(b));
+}
+// 32 lanes x 16 columns of fp32
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+// One 16-column chunk of this lane's row: tokens tok0 .. tok0+15.
+template <int EPI>
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[16], const PairParams& p,
+                                               uint16_t* ycol, bool col_ok, int tok0, float bias_v,
+                                               bool upper) {
+  if (EPI == kEpiStore) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float v = act_fn(__uint_as_float(r[j]) + bias_v, p.act);
+      if (col_ok && tok0 + j < p.m_tok) ycol[static_cast<size_t>(tok0 + j) * p.ldy] = to16(v, p.fmt);
+    }
+  } else {
+    // lanes 0..15 hold gate(f), lanes 16..31 up(f); per token pair the lower half-warp produces
+    // token j, the upper half-warp token j+1.
+#pragma unroll
+    for (int j = 0; j < 16; j += 2) {
+      const uint32_t send = upper ? r[j] : r[j + 1];
+      const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 16);
+      const float g = __uint_as_float(upper ? recv : r[j]);
+      const float u = __uint_as_float(upper ? r[j + 1] : recv);
+      const float sg = __fdividef(1.f, 1.f + __expf(-g));
+      const int t = tok0 + j + (upper ? 1 : 0);
+      if (col_ok && t < p.m_tok) ycol[static_cast<size_t>(t) * p.ldy] = to16((g * sg) * u, p.fmt);
+    }
+  }
 }
 
 template <class C>
@@ -185,7 +241,9 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   const int num_tiles = p.num_m_blks * p.num_n_blks;
-  const int k_iters = (p.K + C::BK - 1) / C::BK;
+  // With BK = 64 the k loop always runs an even number of stages (a trailing stage beyond K loads
+  // zero-filled operands), so metadata loads fall on every second stage without exception.
+  const int k_iters = (C::BK == 128) ? (p.K + 127) / 128 : 2 * ((p.K + 127) / 128);
 
   if (threadIdx.x == 0) {
     *err = 0;
@@ -214,25 +272,23 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     // ------------------------------------------------------------ TMA producer (both CTAs)
     if (elect_one()) {
       const uint32_t leader_full0 = mapa_u32(bar_full, 0);
-      int s = 0;
+      int s = 0, es = 0;
       uint32_t ph = 0;
       bool ok = true;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
         const int m_blk = tile / p.num_n_blks;
         const int n_blk = tile % p.num_n_blks;
-        const int row0 = m_blk * 256 + static_cast<int>(rank) * 128;
+        const int row0 = m_blk * C::ROWS_TILE + static_cast<int>(rank) * C::ROWS_CTA;
         const int tok0 = n_blk * C::BN + static_cast<int>(rank) * C::HALF_N;
-        const int e_tile0 = (m_blk * 2 + static_cast<int>(rank)) * p.k_tiles128;
+        const int e_rt0 = row0 >> 7;   // first 128-row metadata tile of this CTA
         for (int kt = 0; kt < k_iters; ++kt) {
           ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, err, p.status, 1);
           if (!ok) break;
           const bool load_e = (C::BK == 128) || ((kt & 1) == 0);
           const uint32_t full = leader_full0 + 8 * s;
-          if (leader) {
-            // bytes of BOTH CTAs land on this barrier
-            const int kt_e = (C::BK == 128) ? 1 : ((kt & 1) == 0 ? 1 : 0);
-            mbar_arrive_expect_tx(bar_full + 8 * s, 2 * (C::A_BYTES + C::B_BYTES + kt_e * C::E_BYTES));
-          }
+          if (leader)   // bytes of BOTH CTAs land on this barrier
+            mbar_arrive_expect_tx(bar_full + 8 * s,
+                                  2 * (C::A_BYTES + C::B_BYTES + (load_e ? C::E_BYTES : 0)));
           tma_load_2d_pair(sbase + C::OFF_A + s * C::A_BYTES, &tmA, kt * (C::BK / 2), row0, full);
 #pragma unroll
           for (int j = 0; j < C::B_SUBS; ++j)
@@ -240,7 +296,11 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                              kt * C::BK + j * 64, tok0, full);
           if (load_e) {
             const int kt128 = (C::BK == 128) ? kt : (kt >> 1);
-            tma_load_1d_pair(sbase + C::OFF_E + s * C::E_BYTES, &tmE, (e_tile0 + kt128) * 256, full);
+#pragma unroll
+            for (int rs = 0; rs < C::RS; ++rs)
+              tma_load_1d_pair(sbase + C::OFF_E + es * C::E_BYTES + rs * C::E_SUB_BYTES, &tmE,
+                               ((e_rt0 + rs) * p.k_tiles128 + kt128) * 256, full);
+            if (++es == C::E_STAGES) es = 0;
           }
           if (++s == C::STAGES) { s = 0; ph ^= 1; }
         }
@@ -250,7 +310,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     // ------------------------------------------------------------ MMA issuer (even CTA only)
     if (leader && elect_one()) {
       const uint32_t idesc = make_idesc_f16(256, C::BN, p.fmt, true);
-      int s = 0;
+      int s = 0, es = 0;
       uint32_t ph = 0, aph = 0;
       uint32_t e_cols = 0;
       bool ok = true;
@@ -265,22 +325,30 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           tc_fence_after();
           const bool new_e = (C::BK == 128) || ((kt & 1) == 0);
           if (new_e) {
-            e_cols = C::E_COL0 + 4 * s;
-            tc_cp_128x128b_pair(tmem_base + e_cols,
-                                make_smem_desc(sbase + C::OFF_E + s * C::E_BYTES, 0, 128, kSwNone));
+            e_cols = C::E_COL0 + C::E_COLS_STAGE * es;
+#pragma unroll
+            for (int rs = 0; rs < C::RS; ++rs)
+              tc_cp_128x128b_pair(tmem_base + e_cols + 4 * rs,
+                                  make_smem_desc(sbase + C::OFF_E + es * C::E_BYTES + rs * C::E_SUB_BYTES, 0,
+                                                 128, kSwNone));
+            if (++es == C::E_STAGES) es = 0;
           }
           const uint32_t a_addr = sbase + C::OFF_A + s * C::A_BYTES;
           const uint32_t b_addr = sbase + C::OFF_B + s * C::B_BYTES;
 #pragma unroll
           for (int kb = 0; kb < C::MMAS_PER_STAGE; ++kb) {
-            const uint64_t adesc = (C::BK == 64)
-                                       ? make_smem_desc(a_addr + kb * 32, 16, 512, kSw64)
-                                       : make_smem_desc(a_addr + kb * 32, 16, 1024, kSw128);
             const uint64_t bdesc = make_smem_desc(
                 b_addr + (kb >> 1) * C::B_SUB_BYTES + (kb & 1) * 64, 16, 1024, kSw128);
             const int ecol = (C::BK == 128) ? kb : ((kt & 1) * 2 + kb);
-            tc_mma_sp_f16_pair(tmem_base, adesc, bdesc, tmem_base + e_cols + (ecol & ~1),
-                               idesc | (ecol & 1), (kt > 0 || kb > 0) ? 1u : 0u);
+#pragma unroll
+            for (int rs = 0; rs < C::RS; ++rs) {
+              const uint32_t a_sub = a_addr + rs * C::A_SUB_BYTES + kb * 32;
+              const uint64_t adesc = (C::BK == 64) ? make_smem_desc(a_sub, 16, 512, kSw64)
+                                                   : make_smem_desc(a_sub, 16, 1024, kSw128);
+              tc_mma_sp_f16_pair(tmem_base + rs * C::BN, adesc, bdesc,
+                                 tmem_base + e_cols + 4 * rs + (ecol & ~1), idesc | (ecol & 1),
+                                 (kt > 0 || kb > 0) ? 1u : 0u);
+            }
           }
           tc_commit_pair(bar_empty + 8 * s);
           if (++s == C::STAGES) { s = 0; ph ^= 1; }
@@ -292,13 +360,14 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
     const int q = warp & 3;                 // lane quadrant
-    const int hf = (warp - 2) >> 2;         // which half of the token columns
+    const int w2 = (warp - 2) >> 2;         // 0 / 1: column half (RS = 1) or accumulator (RS = 2)
+    const int acc = (C::RS == 1) ? 0 : w2;
+    const int col0 = (C::RS == 1) ? w2 * C::COLS_PER_WARP : 0;
     const uint32_t leader_acce = mapa_u32(bar_acce, 0);
     uint32_t aph = 0;
     bool ok = true;
-    constexpr int NCH = C::COLS_PER_WARP / 32;        // 32-column chunks per warp
-    constexpr int PK = (C::EPI == kEpiSwiGLU) ? 8 : 16;  // packed registers per chunk
-    uint32_t packed[NCH * PK];
+    constexpr int NCH = C::COLS_PER_WARP / 16;
+    const bool upper = lane >= 16;
     for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
       const int m_blk = tile / p.num_n_blks;
       const int n_blk = tile % p.num_n_blks;
@@ -309,75 +378,57 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       if (!ok) break;
       aph ^= 1;
       tc_fence_after();
-      const int row = m_blk * 256 + static_cast<int>(rank) * 128 + q * 32 + lane;  // weight row
-      const int tok_w = n_blk * C::BN + hf * C::COLS_PER_WARP;                      // first token
-      const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + hf * C::COLS_PER_WARP;
+      const int row_w = m_blk * C::ROWS_TILE + static_cast<int>(rank) * C::ROWS_CTA + acc * 128 + q * 32;
+      const int tok_w = n_blk * C::BN + col0;
+      const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * C::BN + col0;
+      uint16_t* ycol;
+      bool col_ok;
       float bias_v = 0.f;
-      if (C::EPI == kEpiStore && p.bias != nullptr && row < p.n_out) bias_v = bias_at(p.bias, row, p.fmt);
-      const bool upper = lane >= 16;
-#pragma unroll
-      for (int c = 0; c < NCH; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_acc + c * 32, r);
-        tmem_ld_wait();
-        if (C::EPI == kEpiStore) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float a = act_fn(__uint_as_float(r[2 * j]) + bias_v, p.act);
-            const float b = act_fn(__uint_as_float(r[2 * j + 1]) + bias_v, p.act);
-            packed[c * PK + j] = pack2(a, b, p.fmt);
-          }
-        } else {
-          // lanes 0..15 hold gate(f), lanes 16..31 up(f); lower half-warp yields even tokens,
-          // upper half-warp odd tokens of the chunk.
-          float h[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const uint32_t send = upper ? r[2 * j] : r[2 * j + 1];
-            const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 16);
-            const float g = __uint_as_float(upper ? recv : r[2 * j]);
-            const float u = __uint_as_float(upper ? r[2 * j + 1] : recv);
-            const float sg = __fdividef(1.f, 1.f + __expf(-g));
-            h[j] = (g * sg) * u;
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) packed[c * PK + j] = pack2(h[2 * j], h[2 * j + 1], p.fmt);
-        }
-      }
-      // accumulator fully drained: hand it back before touching global memory
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_remote(leader_acce);
-
-      uint16_t* y = static_cast<uint16_t*>(p.y);
       if (C::EPI == kEpiStore) {
-        if (row < p.n_out) {
+        const int row = row_w + lane;
+        col_ok = row < p.n_out;
+        ycol = static_cast<uint16_t*>(p.y) + row;
+        if (p.bias != nullptr && col_ok) bias_v = bias_at(p.bias, row, p.fmt);
+      } else {
+        const int f = row_w / 2 + (lane & 15);
+        col_ok = f < p.n_out / 2;
+        ycol = static_cast<uint16_t*>(p.y) + f;
+      }
+      if (C::COLS_PER_WARP <= 128) {
+        // All of this warp's columns fit in registers: issue every tensor-memory load, wait once,
+        // hand the accumulator back, and only then convert and store (off the critical path).
+        uint32_t v[C::COLS_PER_WARP];
 #pragma unroll
-          for (int c = 0; c < NCH; ++c) {
+        for (int c = 0; c < NCH; ++c) {
+          uint32_t(&chunk)[16] = *reinterpret_cast<uint32_t(*)[16]>(&v[c * 16]);
+          tmem_ld_32x16(t_acc + c * 16, chunk);
+        }
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(leader_acce);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int t = tok_w + c * 32 + 2 * j;
-              const uint32_t v = packed[c * PK + j];
-              if (t < p.m_tok) y[static_cast<size_t>(t) * p.ldy + row] = static_cast<uint16_t>(v & 0xFFFF);
-              if (t + 1 < p.m_tok) y[static_cast<size_t>(t + 1) * p.ldy + row] = static_cast<uint16_t>(v >> 16);
-            }
-          }
+        for (int c = 0; c < NCH; ++c) {
+          const uint32_t(&chunk)[16] = *reinterpret_cast<const uint32_t(*)[16]>(&v[c * 16]);
+          epilogue_chunk<C::EPI>(chunk, p, ycol, col_ok, tok_w + c * 16, bias_v, upper);
         }
       } else {
-        // feature index of this lane inside the hidden tensor
-        const int f = (m_blk * 256 + static_cast<int>(rank) * 128 + q * 32) / 2 + (lane & 15);
-        if (f < p.n_out / 2) {
+        uint32_t ra[16], rb[16];
+        tmem_ld_32x16(t_acc, ra);
 #pragma unroll
-          for (int c = 0; c < NCH; ++c) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              // h index 2j, 2j+1 of this half-warp = tokens 4j + par and 4j + 2 + par of the chunk
-              const int t = tok_w + c * 32 + 4 * j + (upper ? 1 : 0);
-              const uint32_t v = packed[c * PK + j];
-              if (t < p.m_tok) y[static_cast<size_t>(t) * p.ldy + f] = static_cast<uint16_t>(v & 0xFFFF);
-              if (t + 2 < p.m_tok) y[static_cast<size_t>(t + 2) * p.ldy + f] = static_cast<uint16_t>(v >> 16);
-            }
+        for (int c = 0; c < NCH; ++c) {
+          tmem_ld_wait();
+          if (c + 1 < NCH) {
+            if (c & 1) tmem_ld_32x16(t_acc + (c + 1) * 16, ra);
+            else tmem_ld_32x16(t_acc + (c + 1) * 16, rb);
+          } else {
+            // every column of this warp's share has been read: hand the accumulator back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(leader_acce);
           }
+          if (c & 1) epilogue_chunk<C::EPI>(rb, p, ycol, col_ok, tok_w + c * 16, bias_v, upper);
+          else epilogue_chunk<C::EPI>(ra, p, ycol, col_ok, tok_w + c * 16, bias_v, upper);
         }
       }
     }
@@ -411,7 +462,7 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
   }
   CUtensorMap tmA, tmB, tmE;
   const uint64_t kc = static_cast<uint64_t>(a.K) / 2;
-  if (!make_map_2d(&tmA, a.values, a.n_out, kc, kc * 2, 128, C::BK / 2,
+  if (!make_map_2d(&tmA, a.values, a.n_out, kc, kc * 2, C::ROWS_CTA, C::BK / 2,
                    C::BK == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, a.fmt))
     return kErrTensorMap;
   if (!make_map_2d(&tmB, a.x, a.m_tok, a.K, static_cast<uint64_t>(a.ldx) * 2, C::HALF_N, 64,
@@ -426,7 +477,7 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
   p.m_tok = a.m_tok;
   p.K = a.K;
   p.ldy = a.ldy;
-  p.num_m_blks = (a.n_out + 255) / 256;
+  p.num_m_blks = (a.n_out + C::ROWS_TILE - 1) / C::ROWS_TILE;
   p.num_n_blks = (a.m_tok + C::BN - 1) / C::BN;
   p.k_tiles128 = (a.K + 127) / 128;
   p.fmt = a.fmt;
@@ -439,6 +490,45 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
 }
 
+// Tile choice.  Cost of a launch in units of "token columns of a 256-row tile at K = 4096":
+// waves x (MMA columns per tile + exposed epilogue).  The 256-row kernel drains its accumulator
+// through registers (about 30 units exposed); the 512-row kernel streams two accumulators out in
+// chunks (about 90 units) but does twice the work per tile and can hit a whole number of waves
+// where 256-row tiles do not (e.g. a 4096-row weight at 4096 tokens: 144 tiles on 74 SM pairs).
+inline int pick_pair_variant(int n_out, int m_tok, int K, int pairs) {
+  const double kscale = 4096.0 / (K > 0 ? K : 4096);
+  auto waves = [&](long tiles) { return static_cast<double>((tiles + pairs - 1) / pairs); };
+  const long t1 = static_cast<long>((n_out + 255) / 256) * ((m_tok + 255) / 256);
+  double best_cost = waves(t1) * (256.0 + 30.0 * kscale);
+  int best = 1256;
+  if (n_out >= 512) {
+    const int cands[4] = {192, 208, 224, 240};
+    for (int bn : cands) {
+      const long t2 = static_cast<long>((n_out + 511) / 512) * ((m_tok + bn - 1) / bn);
+      const double c = waves(t2) * (2.0 * bn + 90.0 * kscale);
+      if (c < best_cost * 0.97) { best_cost = c; best = 2000 + bn; }
+    }
+  }
+  return best;
+}
+
+template <int EPI>
+int dispatch_pair(const SparseGemmArgs& a, cudaStream_t stream) {
+  // force_bn: 1128 / 1256 = 256-row tiles with 128 / 256 tokens; 2192 / 2208 / 2224 / 2240 =
+  // 512-row tiles with that many tokens.  0 = automatic.
+  int v = a.force_bn;
+  if (v == 0) v = pick_pair_variant(a.n_out, a.m_tok, a.K, a.num_sms / 2);
+  switch (v) {
+    case 1128: return launch_pair_cfg<PairCfg<128, 128, 4, 1, EPI>>(a, stream);
+    case 1256: return launch_pair_cfg<PairCfg<256, 128, 4, 1, EPI>>(a, stream);
+    case 2192: return launch_pair_cfg<PairCfg<192, 64, 6, 2, EPI>>(a, stream);
+    case 2208: return launch_pair_cfg<PairCfg<208, 64, 6, 2, EPI>>(a, stream);
+    case 2224: return launch_pair_cfg<PairCfg<224, 64, 6, 2, EPI>>(a, stream);
+    case 2240: return launch_pair_cfg<PairCfg<240, 64, 6, 2, EPI>>(a, stream);
+    default: return kErrInvalid;
+  }
+}
+
 }  // namespace
 
 int launch_sparse_gemm_pair(const SparseGemmArgs& a, cudaStream_t stream) {
@@ -447,14 +537,11 @@ int launch_sparse_gemm_pair(const SparseGemmArgs& a, cudaStream_t stream) {
   if ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.values) |
        reinterpret_cast<uintptr_t>(a.meta)) & 15)
     return kErrInvalid;
-  const int variant = a.force_bn;  // 1256 / 1128: pair kernel with BN 256 / 128
   if (a.epi == kEpiSwiGLU) {
     if (a.n_out % 32 != 0) return kErrInvalid;
-    if (variant == 1128) return launch_pair_cfg<PairCfg<128, 128, 4, kEpiSwiGLU>>(a, stream);
-    return launch_pair_cfg<PairCfg<256, 128, 4, kEpiSwiGLU>>(a, stream);
+    return dispatch_pair<kEpiSwiGLU>(a, stream);
   }
-  if (variant == 1128) return launch_pair_cfg<PairCfg<128, 128, 4, kEpiStore>>(a, stream);
-  return launch_pair_cfg<PairCfg<256, 128, 4, kEpiStore>>(a, stream);
+  return dispatch_pair<kEpiStore>(a, stream);
 }
 
 }  // namespace sfb200

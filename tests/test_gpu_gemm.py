@@ -47,7 +47,8 @@ def _run(R, K, M, dt, bn=0, sigma=0.02, wseed=1, xseed=1234, bias=False, act=Non
 
 
 @pytest.mark.parametrize("bn,R,K,M", [(64, 128, 64, 64), (128, 128, 128, 128), (256, 128, 256, 256),
-                                      (1256, 256, 256, 256), (1128, 256, 128, 128)])
+                                      (1256, 256, 256, 256), (1128, 256, 128, 128), (2208, 512, 256, 208),
+                                      (2240, 1024, 192, 240)])
 def test_identity_activations_reproduce_pruned_weight_exactly(bn, R, K, M):
     dt = "bf16"
     w = seeded_weight(R, K, dt, 3)
@@ -56,10 +57,11 @@ def test_identity_activations_reproduce_pruned_weight_exactly(bn, R, K, M):
     ops.force_token_tile(bn)
     y = ops.sparse_gemm(to_dev(x, dt), cw)
     assert ops.device_status() == 0
-    assert (bits_of(y)[:K].T == o.prune_24(w, dt)["pruned"][:, :M]).all()
+    n = min(K, M)
+    assert (bits_of(y)[:n].T == o.prune_24(w, dt)["pruned"][:, :n]).all()
 
 
-@pytest.mark.parametrize("bn", [32, 64, 128, 192, 256, 1128, 1256])
+@pytest.mark.parametrize("bn", [32, 64, 128, 192, 256, 1128, 1256, 2192, 2208, 2224, 2240])
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
 def test_every_kernel_variant_ragged(bn, dt):
     y, ref = _run(392, 512, 300, dt, bn=bn)
@@ -73,7 +75,7 @@ def test_ragged_token_counts_auto_dispatch(M):
     assert o.rel_err_metrics(y, ref)["floor"] <= REL_TOL
 
 
-@pytest.mark.parametrize("bn", [128, 1256])
+@pytest.mark.parametrize("bn", [128, 1256, 2208])
 @pytest.mark.parametrize("act", [None, "relu", "silu", "gelu"])
 def test_bias_and_activation_epilogues(bn, act):
     y, ref = _run(256, 512, 200, "f16", bn=bn, bias=True, act=act)
