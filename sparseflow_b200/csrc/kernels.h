@@ -72,7 +72,9 @@ int launch_sparse_gemm_pair(const SparseGemmArgs& a, cudaStream_t stream);
 constexpr int kPairMinTokens = 1024;
 
 // ---- small-M (decode) sparse GEMM ----------------------------------------------------------
+// M <= 32 tokens; chosen by launch_sparse_gemm for m_tok <= kSmallMMaxTokens (force_bn == 8 forces it).
 int launch_sparse_gemm_small_m(const SparseGemmArgs& a, cudaStream_t stream);
+constexpr int kSmallMMaxTokens = 8;
 
 // ---- elementwise -----------------------------------------------------------------------------
 // out[m, i] = silu(gu[m, i]) * gu[m, I + i]   (unfused variant, gate|up concatenated along columns)

@@ -37,33 +37,31 @@ struct GroupOut {
 };
 
 // lo = (e0, e1), hi = (e2, e3) as 16-bit patterns; nan_clamp = inf pattern + 1.
+// Key = (min(|w| pattern, nan_clamp) << 2) | tie bits, unique within the group, so the two kept
+// elements are the two largest keys and their positions are the keys' low two bits.  A five
+// comparator network finds them: (a,b) = sort(k0,k1), (c,d) = sort(k2,k3); largest = max(b,d),
+// second = max(min(b,d), max(a,c)).
 template <int TIE>
 __device__ __forceinline__ GroupOut select_group(uint32_t lo, uint32_t hi, uint32_t nan_clamp) {
-  uint32_t k0 = lo & 0x7FFF, k1 = (lo >> 16) & 0x7FFF, k2 = hi & 0x7FFF, k3 = (hi >> 16) & 0x7FFF;
-  k0 = min(k0, nan_clamp);
-  k1 = min(k1, nan_clamp);
-  k2 = min(k2, nan_clamp);
-  k3 = min(k3, nan_clamp);
+  uint32_t k0 = min(lo & 0x7FFFu, nan_clamp), k1 = min((lo >> 16) & 0x7FFFu, nan_clamp);
+  uint32_t k2 = min(hi & 0x7FFFu, nan_clamp), k3 = min((hi >> 16) & 0x7FFFu, nan_clamp);
   if (TIE == kTieHigh) {
-    k0 = (k0 << 2) | 0; k1 = (k1 << 2) | 1; k2 = (k2 << 2) | 2; k3 = (k3 << 2) | 3;
+    k0 = k0 * 4 + 0; k1 = k1 * 4 + 1; k2 = k2 * 4 + 2; k3 = k3 * 4 + 3;
   } else {
-    k0 = (k0 << 2) | 3; k1 = (k1 << 2) | 2; k2 = (k2 << 2) | 1; k3 = (k3 << 2) | 0;
+    k0 = k0 * 4 + 3; k1 = k1 * 4 + 2; k2 = k2 * 4 + 1; k3 = k3 * 4 + 0;
   }
-  // c_ij = key_j > key_i ; keys are distinct
-  const uint32_t c01 = k1 > k0, c02 = k2 > k0, c03 = k3 > k0, c12 = k2 > k1, c13 = k3 > k1,
-                 c23 = k3 > k2;
-  const uint32_t r0 = c01 + c02 + c03;
-  const uint32_t r1 = (1 - c01) + c12 + c13;
-  const uint32_t r2 = (2 - c02 - c12) + c23;
-  const uint32_t r3 = 3 - c03 - c13 - c23;
-  const uint32_t mask = (r0 < 2 ? 1u : 0u) | (r1 < 2 ? 2u : 0u) | (r2 < 2 ? 4u : 0u) |
-                        (r3 < 2 ? 8u : 0u);
-  const uint32_t i0 = __ffs(mask) - 1;
-  const uint32_t i1 = 31 - __clz(mask);
+  const uint32_t a = min(k0, k1), b = max(k0, k1), c = min(k2, k3), d = max(k2, k3);
+  const uint32_t first = max(b, d);
+  const uint32_t second = max(min(b, d), max(a, c));
+  uint32_t pa = first & 3u, pb = second & 3u;
+  if (TIE == kTieLow) { pa = 3u - pa; pb = 3u - pb; }
+  const uint32_t i0 = min(pa, pb), i1 = max(pa, pb);
   GroupOut o;
   o.nib = i0 | (i1 << 2);
-  const uint32_t sel = (2 * i0) | ((2 * i0 + 1) << 4) | ((2 * i1) << 8) | ((2 * i1 + 1) << 12);
+  // byte selectors (2*i, 2*i+1) for both kept elements
+  const uint32_t sel = (i0 * 0x22u + 0x10u) | ((i1 * 0x22u + 0x10u) << 8);
   o.vals = __byte_perm(lo, hi, sel);
+  const uint32_t mask = (1u << i0) | (1u << i1);
   o.lo = lo & ((mask & 1 ? 0xFFFFu : 0u) | (mask & 2 ? 0xFFFF0000u : 0u));
   o.hi = hi & ((mask & 4 ? 0xFFFFu : 0u) | (mask & 8 ? 0xFFFF0000u : 0u));
   return o;

@@ -45,6 +45,19 @@ def test_swiglu_epilogue(bn, dt):
     assert o.rel_err_metrics(o.to_f32(bits_of(h), dt), ref)["floor"] <= REL_TOL
 
 
+@pytest.mark.parametrize("M", [1, 8, 13, 32])
+def test_swiglu_small_m_kernel(M):
+    dt, H, I = "bf16", 1024, 2752
+    wg, wu, _, (pg, pu, _) = _weights(H, I, dt)
+    x = seeded_act(M, H, dt, 4321)
+    cw = ops.compress_gate_up(to_dev(wg, dt), to_dev(wu, dt))
+    ops.force_token_tile(8)
+    h = ops.sparse_gemm_swiglu(to_dev(x, dt), cw)
+    assert ops.device_status() == 0
+    ref = o.silu_mul_ref(o.gemm_ref(x, pg, dt), o.gemm_ref(x, pu, dt))
+    assert o.rel_err_metrics(o.to_f32(bits_of(h), dt), ref)["floor"] <= REL_TOL
+
+
 @pytest.mark.parametrize("H,I,M", [(512, 1408, 100), (4096, 11008, 512)])
 def test_ffn_forward_c_abi_device_and_host(H, I, M):
     """sfb200_ffn_forward / sfb200_ffn_forward_host against the oracle; (4096, 11008, 512) is the

@@ -75,6 +75,20 @@ def test_ragged_token_counts_auto_dispatch(M):
     assert o.rel_err_metrics(y, ref)["floor"] <= REL_TOL
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16, 24, 32])
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+def test_small_m_kernel(M, dt):
+    """Decode kernel (warp-level mma.sp), forced for every M it supports; K with a 64-wide tail."""
+    y, ref = _run(1000, 1024 + 64, M, dt, bn=8, bias=True)
+    assert y.shape == (M, 1000)
+    assert o.rel_err_metrics(y, ref)["floor"] <= REL_TOL
+
+
+def test_small_m_kernel_mistral_down_shape():
+    y, ref = _run(4096, 14336, 8, "bf16", bn=8)
+    assert o.rel_err_metrics(y, ref)["floor"] <= REL_TOL
+
+
 @pytest.mark.parametrize("bn", [128, 1256, 2208])
 @pytest.mark.parametrize("act", [None, "relu", "silu", "gelu"])
 def test_bias_and_activation_epilogues(bn, act):
