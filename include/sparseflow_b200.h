@@ -35,7 +35,8 @@ typedef enum {
   SFB200_ERROR_CUDA = 3,
   SFB200_ERROR_NOT_SUPPORTED = 4,
   SFB200_ERROR_TENSOR_MAP = 8,
-  SFB200_ERROR_DEVICE = 9 /* a kernel gave up on a bounded wait; see sfb200_device_status */
+  SFB200_ERROR_DEVICE = 9, /* a kernel gave up on a bounded wait; see sfb200_device_status */
+  SFB200_ERROR_SCRATCH_TOO_SMALL = 10 /* sfb200_ffn_forward_noalloc: hidden tensor exceeds the static scratch */
 } sfb200_status;
 
 typedef enum { SFB200_F16 = 0, SFB200_BF16 = 1 } sfb200_dtype;
@@ -147,6 +148,23 @@ SFB200_API int sfb200_ffn_forward(const sfb200_ffn_weights* w, const void* x, in
  */
 SFB200_API int sfb200_ffn_forward_host(const sfb200_ffn_weights* w, const void* x_host,
                                        void* out_host, int M, void* stream);
+
+/*
+ * Gated FFN forward for callers that cannot allocate device memory (no counterpart in the
+ * reference).  Same computation and bits as sfb200_ffn_forward, but the M x I hidden tensor lives
+ * in a fixed array inside the library image, so this call and everything under it performs no
+ * cudaMalloc / cudaFree.  Meant for hosts that run under an arena or pool that forbids side
+ * allocations, for latency-critical loops where an allocation could stall, and for embedders with
+ * a fixed device budget.
+ *   - limit: M * I * 2 bytes <= SFB200_NOALLOC_SCRATCH_BYTES, else SFB200_ERROR_SCRATCH_TOO_SMALL;
+ *   - every GPU that loads the library holds the array until the process exits;
+ *   - all calls on a device share the array: calls that overlap on the GPU race, serialise them;
+ *   - the first call on a device resolves the array's device address: issue it before any stream
+ *     capture begins.
+ */
+#define SFB200_NOALLOC_SCRATCH_BYTES (16u << 20)
+SFB200_API int sfb200_ffn_forward_noalloc(const sfb200_ffn_weights* w, const void* x, int ldx, void* out,
+                                          int ldo, int M, void* stream);
 
 /* Tuning hook: force the token tile of the tcgen05 kernels on the current device.  0 = automatic;
  * 32/64/128/192/256 = single-CTA kernel with that tile; 1128/1256 = CTA-pair kernel with a

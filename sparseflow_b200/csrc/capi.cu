@@ -61,6 +61,8 @@ const char* sfb200_status_string(int status) {
     case SFB200_ERROR_NOT_SUPPORTED: return "not supported (needs an sm_100 device)";
     case SFB200_ERROR_TENSOR_MAP: return "TMA tensor map could not be encoded";
     case SFB200_ERROR_DEVICE: return "device-side failure (bounded wait ran out)";
+    case SFB200_ERROR_SCRATCH_TOO_SMALL:
+      return "hidden tensor (M * I * 2 bytes) exceeds the static scratch of sfb200_ffn_forward_noalloc";
     default: return "unknown status";
   }
 }
