@@ -167,8 +167,9 @@ SFB200_API int sfb200_ffn_forward_noalloc(const sfb200_ffn_weights* w, const voi
                                           int ldo, int M, void* stream);
 
 /* Tuning hook: force the token tile of the tcgen05 kernels on the current device.  0 = automatic;
- * 32/64/128/192/256 = single-CTA kernel with that tile; 1128/1256 = CTA-pair kernel with a
- * 128/256-token tile.  No counterpart upstream. */
+ * 8 = decode kernel (M <= 32); 32/64/128/192/256 = single-CTA kernel with that token tile; 1256 =
+ * CTA-pair kernel, 256-row x 256-token tiles; 2192/2208/2224/2240 = CTA-pair kernel, 512-row tiles
+ * with that many tokens.  No counterpart upstream. */
 SFB200_API int sfb200_debug_force_token_tile(int bn);
 
 /* ------------------------------------------------------------------ 2. sf_* runtime API --- */

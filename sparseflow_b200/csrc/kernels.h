@@ -67,7 +67,7 @@ struct SparseGemmArgs {
 };
 int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream);
 // CTA-pair (cta_group::2) variant, 256-row x 256-token tiles; chosen by launch_sparse_gemm for
-// m_tok >= kPairMinTokens.  force_bn 1256 / 1128 selects its token tile explicitly.
+// m_tok >= kPairMinTokens.  force_bn 1256 (256-row tiles) or 2192..2240 (512-row tiles) picks a variant.
 int launch_sparse_gemm_pair(const SparseGemmArgs& a, cudaStream_t stream);
 constexpr int kPairMinTokens = 1024;
 

@@ -383,7 +383,7 @@ int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream) {
     return kErrInvalid;
   // decode-sized token counts: bandwidth kernel on warp-level mma.sp (force with 8, avoid with any other tile)
   if (a.force_bn == 8 || (a.force_bn == 0 && a.m_tok <= kSmallMMaxTokens)) return launch_sparse_gemm_small_m(a, stream);
-  // CTA-pair kernel for prefill-sized token counts (or when forced: 1256 / 1128)
+  // CTA-pair kernel for prefill-sized token counts (or when forced: 1256, 2192..2240)
   if (a.force_bn >= 1000 || (a.force_bn == 0 && a.m_tok >= kPairMinTokens))
     return launch_sparse_gemm_pair(a, stream);
   if (a.epi == kEpiSwiGLU) {

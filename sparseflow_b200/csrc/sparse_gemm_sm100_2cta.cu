@@ -63,6 +63,35 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
       "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(leader_bar)
       : "memory");
 }
+// L2 eviction policies: outputs are written once and never read by this kernel (evict first, so
+// they do not push operand tiles out of L2); the token operand is re-read by every row block
+// (evict last).
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t dst, const CUtensorMap* m, int x, int y,
+                                                      uint32_t leader_bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(leader_bar), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* m, uint32_t src, int x, int y,
+                                                  uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"(
+          reinterpret_cast<uint64_t>(m)),
+      "r"(src), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
 __device__ __forceinline__ void tma_load_1d_pair(uint32_t dst, const CUtensorMap* m, int x,
                                                  uint32_t leader_bar) {
   asm volatile(
@@ -146,7 +175,13 @@ struct PairCfg {
   static constexpr int OFF_A = 0;
   static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
   static constexpr int OFF_E = OFF_B + STAGES * B_BYTES;
-  static constexpr int OFF_BAR = OFF_E + E_STAGES * E_BYTES;
+  // per-warp output staging for the register-drain epilogue (RS = 1): 2 buffers of 16 tokens x
+  // 32 rows (or 16 features for SiLU.mul) of 16-bit values
+  static constexpr int D_ROW_BYTES = (EPI == kEpiSwiGLU) ? 32 : 64;
+  static constexpr int D_BUF_BYTES = 16 * D_ROW_BYTES;
+  static constexpr int OFF_D = OFF_E + E_STAGES * E_BYTES;
+  static constexpr int D_BYTES = (RS == 1) ? 8 * 2 * D_BUF_BYTES : 0;
+  static constexpr int OFF_BAR = OFF_D + D_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
   static constexpr int EPI_WARPS = 8;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
@@ -191,6 +226,37 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
       : "memory");
 }
 
+
+// 16 lanes x 128 columns: thread l gets, for repetition n (8 columns each), r[4n], r[4n+1] =
+// (lane l/4, columns 8n + 2(l%4), +1) and r[4n+2], r[4n+3] = (lane l/4 + 8, same columns): the
+// accumulator-fragment layout of warp-level MMA, which stmatrix can transpose.
+__device__ __forceinline__ void tmem_ld_16x256b_x16(uint32_t taddr, uint32_t (&r)[64]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void stmatrix_x4_trans(uint32_t addr, uint32_t r0, uint32_t r1, uint32_t r2,
+                                                  uint32_t r3) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.trans.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+               "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t pack16(float a, float b, int fmt) {
+  if (fmt == 1) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  const __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ float silu_mul(uint32_t g, uint32_t u) {
+  const float gf = __uint_as_float(g);
+  return (gf * __fdividef(1.f, 1.f + __expf(-gf))) * __uint_as_float(u);
+}
+
 // One 16-column chunk of this lane's row: tokens tok0 .. tok0+15.
 template <int EPI>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[16], const PairParams& p,
@@ -221,7 +287,8 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[16], const Pa
 template <class C>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(C::THREADS, 1)
 sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                        const __grid_constant__ CUtensorMap tmE, const PairParams p) {
+                        const __grid_constant__ CUtensorMap tmE, const __grid_constant__ CUtensorMap tmD,
+                        const PairParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -257,6 +324,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     tma_prefetch_desc(&tmE);
+    tma_prefetch_desc(&tmD);
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(tmem_slot), C::TMEM_COLS);
@@ -272,6 +340,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     // ------------------------------------------------------------ TMA producer (both CTAs)
     if (elect_one()) {
       const uint32_t leader_full0 = mapa_u32(bar_full, 0);
+      const uint64_t pol_keep = l2_policy_evict_last();
       int s = 0, es = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -292,8 +361,8 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           tma_load_2d_pair(sbase + C::OFF_A + s * C::A_BYTES, &tmA, kt * (C::BK / 2), row0, full);
 #pragma unroll
           for (int j = 0; j < C::B_SUBS; ++j)
-            tma_load_2d_pair(sbase + C::OFF_B + s * C::B_BYTES + j * C::B_SUB_BYTES, &tmB,
-                             kt * C::BK + j * 64, tok0, full);
+            tma_load_2d_pair_hint(sbase + C::OFF_B + s * C::B_BYTES + j * C::B_SUB_BYTES, &tmB,
+                                  kt * C::BK + j * 64, tok0, full, pol_keep);
           if (load_e) {
             const int kt128 = (C::BK == 128) ? kt : (kt >> 1);
 #pragma unroll
@@ -364,6 +433,8 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     const int acc = (C::RS == 1) ? 0 : w2;
     const int col0 = (C::RS == 1) ? w2 * C::COLS_PER_WARP : 0;
     const uint32_t leader_acce = mapa_u32(bar_acce, 0);
+    const uint64_t pol_stream = l2_policy_evict_first();
+    (void)pol_stream;
     uint32_t aph = 0;
     bool ok = true;
     constexpr int NCH = C::COLS_PER_WARP / 16;
@@ -394,23 +465,60 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         col_ok = f < p.n_out / 2;
         ycol = static_cast<uint16_t*>(p.y) + f;
       }
-      if (C::COLS_PER_WARP <= 128) {
-        // All of this warp's columns fit in registers: issue every tensor-memory load, wait once,
-        // hand the accumulator back, and only then convert and store (off the critical path).
-        uint32_t v[C::COLS_PER_WARP];
-#pragma unroll
-        for (int c = 0; c < NCH; ++c) {
-          uint32_t(&chunk)[16] = *reinterpret_cast<uint32_t(*)[16]>(&v[c * 16]);
-          tmem_ld_32x16(t_acc + c * 16, chunk);
-        }
+      if constexpr (C::RS == 1) {
+        // Register drain: both 16-lane halves of this warp's quadrant, all its columns, in the
+        // MMA-fragment layout; one wait; accumulator handed back; everything else afterwards.
+        constexpr int NCOL = C::COLS_PER_WARP;          // 128 (or 64)
+        static_assert(NCOL == 128, "register-drain epilogue is written for 128 columns per warp");
+        uint32_t va[64], vb[64];
+        tmem_ld_16x256b_x16(t_acc, va);                                          // lanes q*32 + 0..15
+        tmem_ld_16x256b_x16(t_acc + (static_cast<uint32_t>(16) << 16), vb);      // lanes q*32 + 16..31
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_remote(leader_acce);
+
+        const int g = lane >> 2;
+        const uint32_t stage0 = sbase + C::OFF_D + (warp - 2) * 2 * C::D_BUF_BYTES;
+        // stmatrix row address of this lane: matrix = lane / 8, row in matrix = lane % 8
+        const int mt = lane >> 3, rr = lane & 7;
+        const uint32_t st_off = static_cast<uint32_t>((rr + 8 * (mt >> 1)) * C::D_ROW_BYTES + 16 * (mt & 1));
+        float b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;   // bias of rows g, g+8, 16+g, 24+g
+        if (C::EPI == kEpiStore && p.bias != nullptr) {
+          if (row_w + g < p.n_out) b0 = bias_at(p.bias, row_w + g, p.fmt);
+          if (row_w + g + 8 < p.n_out) b1 = bias_at(p.bias, row_w + g + 8, p.fmt);
+          if (row_w + g + 16 < p.n_out) b2 = bias_at(p.bias, row_w + g + 16, p.fmt);
+          if (row_w + g + 24 < p.n_out) b3 = bias_at(p.bias, row_w + g + 24, p.fmt);
+        }
+        const int out_x = (C::EPI == kEpiSwiGLU) ? row_w / 2 : row_w;   // first output column of this warp
 #pragma unroll
-        for (int c = 0; c < NCH; ++c) {
-          const uint32_t(&chunk)[16] = *reinterpret_cast<const uint32_t(*)[16]>(&v[c * 16]);
-          epilogue_chunk<C::EPI>(chunk, p, ycol, col_ok, tok_w + c * 16, bias_v, upper);
+        for (int c = 0; c < NCOL / 16; ++c) {
+          const uint32_t stage = stage0 + (c & 1) * C::D_BUF_BYTES;
+          if (lane == 0) tma_store_wait_read<1>();     // the buffer's previous store has read it
+          __syncwarp();
+          const int o = 8 * c;                          // registers of this 16-column chunk
+          if (C::EPI == kEpiSwiGLU) {
+            // half 0 = 16 gate rows, half 1 = the 16 matching up rows: pairing is in-thread
+            const uint32_t h0 = pack16(silu_mul(va[o + 0], vb[o + 0]), silu_mul(va[o + 1], vb[o + 1]), p.fmt);
+            const uint32_t h1 = pack16(silu_mul(va[o + 2], vb[o + 2]), silu_mul(va[o + 3], vb[o + 3]), p.fmt);
+            const uint32_t h2 = pack16(silu_mul(va[o + 4], vb[o + 4]), silu_mul(va[o + 5], vb[o + 5]), p.fmt);
+            const uint32_t h3 = pack16(silu_mul(va[o + 6], vb[o + 6]), silu_mul(va[o + 7], vb[o + 7]), p.fmt);
+            stmatrix_x4_trans(stage + st_off, h0, h1, h2, h3);
+          } else {
+            auto f = [&](uint32_t v, float bias) { return act_fn(__uint_as_float(v) + bias, p.act); };
+            stmatrix_x4_trans(stage + st_off,
+                              pack16(f(va[o + 0], b0), f(va[o + 1], b0), p.fmt), pack16(f(va[o + 2], b1), f(va[o + 3], b1), p.fmt),
+                              pack16(f(va[o + 4], b0), f(va[o + 5], b0), p.fmt), pack16(f(va[o + 6], b1), f(va[o + 7], b1), p.fmt));
+            stmatrix_x4_trans(stage + st_off + 32,
+                              pack16(f(vb[o + 0], b2), f(vb[o + 1], b2), p.fmt), pack16(f(vb[o + 2], b3), f(vb[o + 3], b3), p.fmt),
+                              pack16(f(vb[o + 4], b2), f(vb[o + 5], b2), p.fmt), pack16(f(vb[o + 6], b3), f(vb[o + 7], b3), p.fmt));
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && tok_w + c * 16 < p.m_tok) {
+            tma_store_2d_hint(&tmD, stage, out_x, tok_w + c * 16, pol_stream);
+            tma_store_commit();
+          }
         }
       } else {
         uint32_t ra[16], rb[16];
@@ -432,6 +540,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         }
       }
     }
+    if (C::RS == 1 && lane == 0) tma_store_wait_all<0>();
   }
 
   // ------------------------------------------------------------ teardown
@@ -460,7 +569,7 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
       return kErrCuda;
     attr_set[dev] = true;
   }
-  CUtensorMap tmA, tmB, tmE;
+  CUtensorMap tmA, tmB, tmE, tmD;
   const uint64_t kc = static_cast<uint64_t>(a.K) / 2;
   if (!make_map_2d(&tmA, a.values, a.n_out, kc, kc * 2, C::ROWS_CTA, C::BK / 2,
                    C::BK == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, a.fmt))
@@ -469,6 +578,12 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
                    CU_TENSOR_MAP_SWIZZLE_128B, a.fmt))
     return kErrTensorMap;
   if (!make_map_1d_u64(&tmE, a.meta, meta_bytes(a.n_out, a.K) / 8, 256)) return kErrTensorMap;
+  {
+    const int out_cols = (C::EPI == kEpiSwiGLU) ? a.n_out / 2 : a.n_out;
+    if (!make_map_2d(&tmD, a.y, a.m_tok, out_cols, static_cast<uint64_t>(a.ldy) * 2, 16, C::D_ROW_BYTES / 2,
+                     CU_TENSOR_MAP_SWIZZLE_NONE, a.fmt))
+      return kErrTensorMap;
+  }
   PairParams p;
   p.bias = a.bias;
   p.y = a.y;
@@ -486,7 +601,7 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
   int pairs = a.num_sms / 2;
   if (pairs > tiles) pairs = tiles;
   if (pairs < 1) pairs = 1;
-  sparse_gemm_pair_kernel<C><<<2 * pairs, C::THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmE, p);
+  sparse_gemm_pair_kernel<C><<<2 * pairs, C::THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmE, tmD, p);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
 }
 
@@ -514,12 +629,11 @@ inline int pick_pair_variant(int n_out, int m_tok, int K, int pairs) {
 
 template <int EPI>
 int dispatch_pair(const SparseGemmArgs& a, cudaStream_t stream) {
-  // force_bn: 1128 / 1256 = 256-row tiles with 128 / 256 tokens; 2192 / 2208 / 2224 / 2240 =
+  // force_bn: 1256 = 256-row tiles with 256 tokens; 2192 / 2208 / 2224 / 2240 =
   // 512-row tiles with that many tokens.  0 = automatic.
   int v = a.force_bn;
   if (v == 0) v = pick_pair_variant(a.n_out, a.m_tok, a.K, a.num_sms / 2);
   switch (v) {
-    case 1128: return launch_pair_cfg<PairCfg<128, 128, 4, 1, EPI>>(a, stream);
     case 1256: return launch_pair_cfg<PairCfg<256, 128, 4, 1, EPI>>(a, stream);
     case 2192: return launch_pair_cfg<PairCfg<192, 64, 6, 2, EPI>>(a, stream);
     case 2208: return launch_pair_cfg<PairCfg<208, 64, 6, 2, EPI>>(a, stream);
@@ -535,10 +649,11 @@ int launch_sparse_gemm_pair(const SparseGemmArgs& a, cudaStream_t stream) {
   if (a.K % 64 != 0 || a.K <= 0 || a.m_tok <= 0 || a.n_out <= 0) return kErrInvalid;
   if (a.n_out % 8 != 0 || a.ldx % 8 != 0) return kErrInvalid;
   if ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.values) |
-       reinterpret_cast<uintptr_t>(a.meta)) & 15)
+       reinterpret_cast<uintptr_t>(a.meta) | reinterpret_cast<uintptr_t>(a.y)) & 15)
     return kErrInvalid;
+  if (a.ldy % 8 != 0) return kErrInvalid;
   if (a.epi == kEpiSwiGLU) {
-    if (a.n_out % 32 != 0) return kErrInvalid;
+    if (a.n_out % 32 != 0 || (a.n_out / 2) % 8 != 0) return kErrInvalid;
     return dispatch_pair<kEpiSwiGLU>(a, stream);
   }
   return dispatch_pair<kEpiStore>(a, stream);
