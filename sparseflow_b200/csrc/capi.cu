@@ -238,10 +238,54 @@ int sfb200_ffn_forward_host(const sfb200_ffn_weights* w, const void* x_host, voi
       s->stage_h_bytes = hb;
     }
   }
-  if (cudaMemcpyAsync(s->stage_x, x_host, xb, cudaMemcpyHostToDevice, st) != cudaSuccess) return kErrCuda;
-  int rc = sfb200_ffn_forward(w, s->stage_x, w->H, s->stage_h, s->stage_o, w->H, M, stream);
-  if (rc != kOk) return rc;
-  if (cudaMemcpyAsync(out_host, s->stage_o, xb, cudaMemcpyDeviceToHost, st) != cudaSuccess) return kErrCuda;
+  // Pipeline over token chunks: host->device copy of chunk i+1, FFN of chunk i and device->host
+  // copy of chunk i-1 run concurrently (copy-in stream, the caller's stream, copy-out stream).
+  {
+    std::lock_guard<std::mutex> lk(g_state_mu);
+    if (!s->pipe_ready) {
+      bool ok = cudaStreamCreateWithFlags(&s->s_in, cudaStreamNonBlocking) == cudaSuccess &&
+                cudaStreamCreateWithFlags(&s->s_out, cudaStreamNonBlocking) == cudaSuccess &&
+                cudaEventCreateWithFlags(&s->ev_start, cudaEventDisableTiming) == cudaSuccess &&
+                cudaEventCreateWithFlags(&s->ev_done, cudaEventDisableTiming) == cudaSuccess;
+      for (int i = 0; ok && i < DeviceState::kMaxChunks; ++i)
+        ok = cudaEventCreateWithFlags(&s->ev_in[i], cudaEventDisableTiming) == cudaSuccess &&
+             cudaEventCreateWithFlags(&s->ev_cmp[i], cudaEventDisableTiming) == cudaSuccess;
+      if (!ok) {
+        cudaGetLastError();
+        return kErrCuda;
+      }
+      s->pipe_ready = true;
+    }
+  }
+  int chunks = M / 1024;
+  if (chunks < 1) chunks = 1;
+  if (chunks > DeviceState::kMaxChunks) chunks = DeviceState::kMaxChunks;
+  const int rows_per = ((M + chunks - 1) / chunks + 7) & ~7;
+  const size_t row_x = static_cast<size_t>(w->H) * 2, row_h = static_cast<size_t>(w->I) * 2;
+  if (cudaEventRecord(s->ev_start, st) != cudaSuccess) return kErrCuda;
+  if (cudaStreamWaitEvent(s->s_in, s->ev_start, 0) != cudaSuccess) return kErrCuda;
+  if (cudaStreamWaitEvent(s->s_out, s->ev_start, 0) != cudaSuccess) return kErrCuda;
+  int c = 0;
+  for (int r0 = 0; r0 < M; r0 += rows_per, ++c) {
+    const int rows = (M - r0 < rows_per) ? M - r0 : rows_per;
+    uint8_t* xd = static_cast<uint8_t*>(s->stage_x) + r0 * row_x;
+    uint8_t* od = static_cast<uint8_t*>(s->stage_o) + r0 * row_x;
+    uint8_t* hd = static_cast<uint8_t*>(s->stage_h) + r0 * row_h;
+    if (cudaMemcpyAsync(xd, static_cast<const uint8_t*>(x_host) + r0 * row_x, rows * row_x,
+                        cudaMemcpyHostToDevice, s->s_in) != cudaSuccess)
+      return kErrCuda;
+    cudaEventRecord(s->ev_in[c], s->s_in);
+    cudaStreamWaitEvent(st, s->ev_in[c], 0);
+    const int rc = sfb200_ffn_forward(w, xd, w->H, hd, od, w->H, rows, stream);
+    if (rc != kOk) return rc;
+    cudaEventRecord(s->ev_cmp[c], st);
+    cudaStreamWaitEvent(s->s_out, s->ev_cmp[c], 0);
+    if (cudaMemcpyAsync(static_cast<uint8_t*>(out_host) + r0 * row_x, od, rows * row_x, cudaMemcpyDeviceToHost,
+                        s->s_out) != cudaSuccess)
+      return kErrCuda;
+  }
+  cudaEventRecord(s->ev_done, s->s_out);
+  cudaStreamWaitEvent(st, s->ev_done, 0);
   if (cudaStreamSynchronize(st) != cudaSuccess) return kErrCuda;
   return kOk;
 }

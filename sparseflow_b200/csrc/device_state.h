@@ -1,5 +1,6 @@
 // Per-device library state: status word, device facts, staging buffers of the host-buffer FFN call.
 #pragma once
+#include <cuda_runtime.h>
 #include <stddef.h>
 
 namespace sfb200 {
@@ -18,6 +19,12 @@ struct DeviceState {
   void* stage_h = nullptr;
   size_t stage_x_bytes = 0;
   size_t stage_h_bytes = 0;
+  // host-buffer FFN pipeline: copy-in / copy-out streams and per-chunk events
+  static constexpr int kMaxChunks = 8;
+  cudaStream_t s_in = nullptr, s_out = nullptr;
+  cudaEvent_t ev_start = nullptr, ev_done = nullptr;
+  cudaEvent_t ev_in[kMaxChunks] = {}, ev_cmp[kMaxChunks] = {};
+  bool pipe_ready = false;
 };
 
 // State of the current device, created on first use.  Returns nullptr and sets *err when there is
