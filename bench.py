@@ -38,7 +38,9 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate|up kernel, from the ncu
 # capture summarised in profiles/ (None until a capture of that workload exists).
 NCU_TRAFFIC_BYTES = {
-    "llama7b_ffn": None,
+    # profiles/sparse_gemm_pair_gate_up_llama7b.md: 149.2 MB measured at M = 2048, scaled to M = 4096
+    # (weights fixed, activations and outputs proportional to M)
+    "llama7b_ffn": 196.2e6,
 }
 
 

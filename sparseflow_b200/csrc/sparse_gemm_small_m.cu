@@ -30,11 +30,11 @@ namespace sfb200 {
 namespace {
 
 constexpr int kWarps = 8;
-constexpr int kStages = 4;
+__host__ __device__ constexpr int kStagesFor(int sl) { return sl == 1 ? 4 : 4; }   // ring depth (deeper rings measured no faster)
 constexpr int kRowPitch = 144;                        // 128 B of values + 16 B pad: conflict-free ldmatrix
 constexpr int kValBytes = 16 * kRowPitch;             // one 16-row x 128-logical-K chunk of values
 constexpr int kStageBytes = kValBytes + 256;          // + the slab's metadata for that K tile (16 lanes x 16 B)
-constexpr int kWarpSmem = kStages * kStageBytes;      // 10240 B
+__host__ __device__ constexpr int kWarpSmemFor(int sl) { return kStagesFor(sl) * sl * kStageBytes; }
 constexpr int kMaxNT = 4;                             // up to 32 tokens
 
 struct SmallParams {
@@ -95,10 +95,12 @@ template <int NT, int SL, bool SWIGLU, bool BF16>
 __global__ void __launch_bounds__(kWarps * 32) sparse_gemm_small_m_kernel(const SmallParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   constexpr int kRows = 16 * SL;
-  float* red = reinterpret_cast<float*>(smem + kWarps * SL * kWarpSmem);   // [kWarps][kRows][8*NT]
+  constexpr int kStages = kStagesFor(SL);
+  constexpr int kWarpBytes = kWarpSmemFor(SL);
+  float* red = reinterpret_cast<float*>(smem + kWarps * kWarpBytes);   // [kWarps][kRows][8*NT]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const uint32_t wbase = static_cast<uint32_t>(__cvta_generic_to_shared(smem + warp * SL * kWarpSmem));
+  const uint32_t wbase = static_cast<uint32_t>(__cvta_generic_to_shared(smem + warp * kWarpBytes));
 
   // this warp's share of the 128-wide K tiles
   const int kt_lo = (p.k_tiles128 * warp) / kWarps;
@@ -109,7 +111,7 @@ __global__ void __launch_bounds__(kWarps * 32) sparse_gemm_small_m_kernel(const 
   // X fragment cache of this warp's K slice: xs[(k-step * NT + n) * 32 + lane] = (b0, b1, b2, b3)
   uint4* xs = nullptr;
   if (p.xs_ksteps > 0) {
-    uint8_t* xs_base = smem + kWarps * SL * kWarpSmem + 2 * kWarps * kRows * 8 * NT * 4;
+    uint8_t* xs_base = smem + kWarps * kWarpBytes + 2 * kWarps * kRows * 8 * NT * 4;
     xs = reinterpret_cast<uint4*>(xs_base) + static_cast<size_t>(warp) * p.xs_ksteps * NT * 32;
     for (int ks = 0; ks < n_kt * 4; ++ks) {
       const int k0 = (kt_lo * 4 + ks) * 32;
@@ -132,13 +134,14 @@ __global__ void __launch_bounds__(kWarps * 32) sparse_gemm_small_m_kernel(const 
   const int my_slabs = (p.num_slabs - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
                        static_cast<int>(gridDim.x);
   const int total_items = my_slabs * n_kt;
-  int issued = 0, consumed = 0;
+  // issue cursor (slab, k-tile, ring slot) advances incrementally: no divisions in the loop
+  int issued = 0, iss_slab = blockIdx.x, iss_kt = 0, iss_slot = 0, con_slot = 0;
   auto issue_next = [&]() {
     if (issued < total_items) {
-      const int it_slab = blockIdx.x + (issued / n_kt) * gridDim.x;
-      const int kc0 = (kt_lo + issued % n_kt) * 64;   // first compressed element of the chunk
-      const int r0 = it_slab * kRows;
-      const uint32_t sdst = wbase + (issued % kStages) * SL * kStageBytes;
+      const int kt = kt_lo + iss_kt;
+      const int kc0 = kt * 64;   // first compressed element of the chunk
+      const int r0 = iss_slab * kRows;
+      const uint32_t sdst = wbase + iss_slot * SL * kStageBytes;
 #pragma unroll
       for (int j = 0; j < 4 * SL; ++j) {
         const int idx = j * 32 + lane;
@@ -151,14 +154,15 @@ __global__ void __launch_bounds__(kWarps * 32) sparse_gemm_small_m_kernel(const 
       if (lane < 16 * SL) {   // metadata: lanes [16*m2, 16*m2+16) of the 128-lane tile, 16 B each
         const int sl = lane >> 4, ln = lane & 15;
         const int r16 = r0 + 16 * sl;
-        const int kt = kt_lo + issued % n_kt;
         const uint32_t* mp = p.meta + ((static_cast<size_t>(r16 >> 7) * p.k_tiles128 + kt) * 128 +
                                        (((r16 & 127) >> 4) * 16 + ln)) * 4;
         cp_async16(sdst + SL * kValBytes + sl * 256 + ln * 16, mp, true);
       }
+      if (++iss_kt == n_kt) { iss_kt = 0; iss_slab += gridDim.x; }
     }
     cp_async_commit();
     ++issued;
+    if (++iss_slot == kStages) iss_slot = 0;
   };
 #pragma unroll
   for (int i = 0; i < kStages - 1; ++i) issue_next();
@@ -198,9 +202,9 @@ __global__ void __launch_bounds__(kWarps * 32) sparse_gemm_small_m_kernel(const 
       __syncwarp();
       // metadata: lanes with t < 2 hold the four words (one per 32-wide K block) of rows g, g+8
       uint32_t e4[SL][4];
-      const uint32_t sA = wbase + (consumed % kStages) * SL * kStageBytes;
-      const uint8_t* sA_gen = smem + warp * SL * kWarpSmem + (consumed % kStages) * SL * kStageBytes;
-      ++consumed;
+      const uint32_t sA = wbase + con_slot * SL * kStageBytes;
+      const uint8_t* sA_gen = smem + warp * kWarpBytes + con_slot * SL * kStageBytes;
+      if (++con_slot == kStages) con_slot = 0;
 #pragma unroll
       for (int sl = 0; sl < SL; ++sl) {
         // lane (g, t < 2) takes tile lane g + 8t: rows g and g+8, K half t
@@ -289,7 +293,7 @@ __global__ void __launch_bounds__(kWarps * 32) sparse_gemm_small_m_kernel(const 
 
 template <int NT, int SL, bool SWIGLU, bool BF16>
 int launch_nt(SmallParams p, int num_sms, cudaStream_t stream) {
-  int smem = kWarps * SL * kWarpSmem + 2 * kWarps * 16 * SL * 8 * NT * 4;
+  int smem = kWarps * kWarpSmemFor(SL) + 2 * kWarps * 16 * SL * 8 * NT * 4;
   {  // X fragment cache if it leaves room (k-steps per warp x NT x 512 B x 8 warps)
     const int ksteps = ((p.k_tiles128 + kWarps - 1) / kWarps) * 4;
     const int xs_bytes = kWarps * ksteps * NT * 512;
