@@ -52,7 +52,9 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama7b_ffn", choices=sorted(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=0, help="override the token count")
-    ap.add_argument("--chunks", type=int, default=1, help="token chunks for all-reduce overlap (N > 1)")
+    ap.add_argument("--chunks", type=int, default=1, help="token chunks for all-reduce overlap (N > 1, --tp nccl)")
+    ap.add_argument("--tp", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: exchange step fused into the kernels over peer memory, or NCCL all-reduce")
     ap.add_argument("--cpu-tokens", type=int, default=0, help="tokens of the CPU baseline sample (0 = auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
@@ -276,10 +278,28 @@ def main():
     prune_ms = t0.elapsed_time(t1) / 5
     prune_gbs = H * I * 3.125 / (prune_ms * 1e-3) / 1e9
 
-    ffn = parallel.TensorParallelFFN(wg, wu, wd, chunks=args.chunks)
+    tp_mode = "single GPU"
+    ffn = None
+    if world > 1 and args.tp == "fused":
+        try:
+            ffn = parallel.FusedTensorParallelFFN(wg, wu, wd, max_tokens=M)
+            tp_mode = "fused: reduce-scatter in the down-GEMM epilogue (TMA stores to peer memory), all-gather in the reduction kernel"
+        except Exception as exc:      # symmetric memory unavailable on this box: NCCL path
+            sys.stderr.write(f"fused tensor-parallel path unavailable ({exc!r}); using NCCL all-reduce\n")
+            ffn = None
+    if ffn is None:
+        ffn = parallel.TensorParallelFFN(wg, wu, wd, chunks=args.chunks)
+        if world > 1:
+            tp_mode = f"NCCL all-reduce after the down GEMM, {args.chunks} chunk(s)"
+    fused_tp = isinstance(ffn, parallel.FusedTensorParallelFFN)
     del wg, wu
     hidden = torch.empty((M, ffn.Ip), dtype=dt, device=dev)
     out = torch.empty((M, H), dtype=dt, device=dev)
+
+    def run_step():
+        if fused_tp:
+            return ffn.forward(x)
+        return ffn.forward(x, hidden, out)
 
     def barrier():
         if world > 1:
@@ -288,7 +308,7 @@ def main():
 
     # ---- warm-up
     for _ in range(max(3, args.warmup)):
-        ffn.forward(x, hidden, out)
+        run_step()
     barrier()
     ops.device_status()
 
@@ -310,7 +330,7 @@ def main():
             ffn.kernel_launches += 2
     else:
         for k in range(args.steps):
-            ffn.forward(x, hidden, out)
+            run_step()
     s1.record()
     barrier()
     clocks = sampler.stop()
@@ -370,9 +390,9 @@ def main():
         e0.record()
         for _ in range(args.steps):
             x.copy_(x_host, non_blocking=True)
-            ffn.forward(x, hidden, out)
+            res = run_step()
             if rank == 0:
-                out_host.copy_(out, non_blocking=True)
+                out_host.copy_(res, non_blocking=True)
             torch.cuda.current_stream().synchronize()
         e1.record(); barrier()
         t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
@@ -429,7 +449,7 @@ def main():
             "data": "synthetic",
             "config": {"workload": f"{args.workload}: hidden {H}, intermediate {I}, {M} tokens, bf16, 2:4-pruned gate/up/down",
                        "hidden": H, "intermediate": I, "tokens": M,
-                       "parallelism": "single GPU" if world == 1 else f"tp{world}: column-parallel gate/up, row-parallel down, NCCL all-reduce, {args.chunks} chunk(s)",
+                       "parallelism": "single GPU" if world == 1 else f"tp{world}: column-parallel gate/up, row-parallel down; {tp_mode}",
                        "l2": "no flush: per-step working set (weights 152 MB + activations 157 MB for the default workload) exceeds the 126 MB L2"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
             "roofline": roof, "cpu_baseline": cpu, "dense_cublas": dense,

@@ -150,6 +150,25 @@ SFB200_API int sfb200_ffn_forward_host(const sfb200_ffn_weights* w, const void* 
                                        void* out_host, int M, void* stream);
 
 /*
+ * Tensor-parallel building blocks (no counterpart in the reference, which has no distributed code).
+ * Row-parallel GEMM with the reduce-scatter fused into its epilogue: rank r computes its partial
+ * Y_r[M, N] = X_r . W_r^T and stores token block o (tok_per_owner tokens, a multiple of 16) straight
+ * into peer_slots[o], rank o's receive slot for rank r ([tok_per_owner, N], peer-mapped memory, e.g.
+ * a torch symmetric-memory buffer).  peer_slots is a HOST array of tp device pointers.  tp <= 8.
+ */
+SFB200_API int sfb200_sparse_gemm_scatter(const void* x, int ldx, const void* values, const void* meta,
+                                          void* const* peer_slots, int tp, int tok_per_owner, int M, int N,
+                                          int K, int dtype, void* stream);
+/*
+ * slots[tp][rows, cols] (local) are summed in fp32 (+ bias) and the result is written to
+ * peer_out_blocks[d] for every rank d (this rank's token block inside rank d's output tensor): the
+ * all-gather fused into the reduction.  Callers order the two kernels across ranks with
+ * stream-ordered barriers; neither kernel waits on another GPU.
+ */
+SFB200_API int sfb200_reduce_allgather(const void* slots, int tp, int rows, int cols,
+                                       void* const* peer_out_blocks, int dtype, const void* bias, void* stream);
+
+/*
  * Gated FFN forward for callers that cannot allocate device memory (no counterpart in the
  * reference).  Same computation and bits as sfb200_ffn_forward, but the M x I hidden tensor lives
  * in a fixed array inside the library image, so this call and everything under it performs no

@@ -290,6 +290,40 @@ int sfb200_ffn_forward_host(const sfb200_ffn_weights* w, const void* x_host, voi
   return kOk;
 }
 
+int sfb200_sparse_gemm_scatter(const void* x, int ldx, const void* values, const void* meta,
+                               void* const* peer_slots, int tp, int tok_per_owner, int M, int N, int K, int dtype,
+                               void* stream) {
+  int err = kOk;
+  DeviceState* s = device_state(&err);
+  if (!s) return err;
+  if (!x || !values || !meta || !peer_slots) return kErrInvalid;
+  if (dtype != kF16 && dtype != kBF16) return kErrInvalid;
+  SparseGemmArgs a{};
+  a.x = x;
+  a.values = values;
+  a.meta = meta;
+  a.status = s->status;
+  a.m_tok = M;
+  a.n_out = N;
+  a.K = K;
+  a.ldx = ldx;
+  a.ldy = N;
+  a.fmt = dtype;
+  a.epi = kEpiStore;
+  a.act = kActNone;
+  a.num_sms = s->num_sms;
+  return launch_sparse_gemm_pair_scatter(a, peer_slots, tp, tok_per_owner, static_cast<cudaStream_t>(stream));
+}
+
+int sfb200_reduce_allgather(const void* slots, int tp, int rows, int cols, void* const* peer_out_blocks, int dtype,
+                            const void* bias, void* stream) {
+  int err = kOk;
+  if (!device_state(&err)) return err;
+  if (!peer_out_blocks) return kErrInvalid;
+  return launch_reduce_allgather(slots, tp, rows, cols, peer_out_blocks, dtype, bias,
+                                 static_cast<cudaStream_t>(stream));
+}
+
 /* Test / tuning hook: force the token tile of the tcgen05 kernel (0 = automatic). */
 SFB200_API int sfb200_debug_force_token_tile(int bn) {
   int err = kOk;

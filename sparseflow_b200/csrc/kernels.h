@@ -70,6 +70,15 @@ int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream);
 // m_tok >= kPairMinTokens.  force_bn 1256 (256-row tiles) or 2192..2240 (512-row tiles) picks a variant.
 int launch_sparse_gemm_pair(const SparseGemmArgs& a, cudaStream_t stream);
 constexpr int kPairMinTokens = 1024;
+// Row-parallel GEMM of a tensor-parallel FFN with the reduce-scatter fused into the epilogue:
+// token block o of this rank's partial output is stored into peer_slots[o] (rank o's receive slot
+// for this rank, [tok_per_owner, n_out], peer-mapped memory).
+int launch_sparse_gemm_pair_scatter(const SparseGemmArgs& a, void* const* peer_slots, int tp, int tok_per_owner,
+                                    cudaStream_t stream);
+// out_block = sum over tp receive slots (fp32), written to every rank's output at this rank's token
+// block (all-gather fused into the reduction).  slots: [tp][rows, cols] contiguous, local.
+int launch_reduce_allgather(const void* slots, int tp, int rows, int cols, void* const* peer_out_blocks, int fmt,
+                            const void* bias, cudaStream_t stream);
 
 // ---- small-M (decode) sparse GEMM ----------------------------------------------------------
 // M <= 32 tokens; chosen by launch_sparse_gemm for m_tok <= kSmallMMaxTokens (force_bn == 8 forces it).

@@ -144,6 +144,13 @@ struct PairParams {
   int num_m_blks, num_n_blks;   // (256*RS)-row / BN-token tiles
   int k_tiles128;
   int fmt, act;
+  int tok_per_owner;   // scatter epilogue: tokens owned by each rank (0 = plain output)
+};
+
+// Output tensor maps of the scatter epilogue: one per destination rank (its receive slot for this
+// rank's partial sums, mapped into this GPU's address space).
+struct ScatterMaps {
+  CUtensorMap m[8];
 };
 
 template <int BN_, int BK_, int STAGES_, int RS_, int EPI_>
@@ -284,11 +291,10 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[16], const Pa
   }
 }
 
-template <class C>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(C::THREADS, 1)
-sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                        const __grid_constant__ CUtensorMap tmE, const __grid_constant__ CUtensorMap tmD,
-                        const PairParams p) {
+template <class C, bool SCATTER>
+__device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const CUtensorMap& tmB,
+                                                 const CUtensorMap& tmE, const CUtensorMap& tmD,
+                                                 const ScatterMaps* tmS, const PairParams& p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -516,7 +522,15 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0 && tok_w + c * 16 < p.m_tok) {
-            tma_store_2d_hint(&tmD, stage, out_x, tok_w + c * 16, pol_stream);
+            const int t0 = tok_w + c * 16;
+            if (SCATTER) {
+              // reduce-scatter fused into the GEMM: the chunk goes to the rank that owns these
+              // tokens, into the slot reserved for this rank's partial sums (a store over NVLink)
+              const int owner = t0 / p.tok_per_owner;
+              tma_store_2d(&tmS->m[owner], stage, out_x, t0 - owner * p.tok_per_owner);
+            } else {
+              tma_store_2d_hint(&tmD, stage, out_x, t0, pol_stream);
+            }
             tma_store_commit();
           }
         }
@@ -559,6 +573,23 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 }
 
 template <class C>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(C::THREADS, 1)
+sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                        const __grid_constant__ CUtensorMap tmE, const __grid_constant__ CUtensorMap tmD,
+                        const PairParams p) {
+  pair_kernel_body<C, false>(tmA, tmB, tmE, tmD, nullptr, p);
+}
+
+// Same kernel with the scatter epilogue (tensor-parallel row-parallel GEMM).
+template <class C>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(C::THREADS, 1)
+sparse_gemm_pair_scatter_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                                const __grid_constant__ CUtensorMap tmE, const __grid_constant__ ScatterMaps tmS,
+                                const PairParams p) {
+  pair_kernel_body<C, true>(tmA, tmB, tmE, tmS.m[0], &tmS, p);
+}
+
+template <class C>
 int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
   static bool attr_set[16] = {};
   int dev = 0;
@@ -597,6 +628,7 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
   p.k_tiles128 = (a.K + 127) / 128;
   p.fmt = a.fmt;
   p.act = a.act;
+  p.tok_per_owner = 0;
   const int tiles = p.num_m_blks * p.num_n_blks;
   int pairs = a.num_sms / 2;
   if (pairs > tiles) pairs = tiles;
@@ -644,6 +676,59 @@ int dispatch_pair(const SparseGemmArgs& a, cudaStream_t stream) {
 }
 
 }  // namespace
+
+int launch_sparse_gemm_pair_scatter(const SparseGemmArgs& a, void* const* peer_slots, int tp, int tok_per_owner,
+                                    cudaStream_t stream) {
+  using C = PairCfg<256, 128, 4, 1, kEpiStore>;
+  if (a.K % 64 != 0 || a.m_tok <= 0 || a.n_out <= 0 || a.n_out % 8 != 0 || a.ldx % 8 != 0) return kErrInvalid;
+  if (tp < 2 || tp > 8 || tok_per_owner <= 0 || tok_per_owner % 16 != 0 || tok_per_owner * tp < a.m_tok)
+    return kErrInvalid;
+  static bool attr_set[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 16 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(sparse_gemm_pair_scatter_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             C::SMEM_BYTES) != cudaSuccess)
+      return kErrCuda;
+    attr_set[dev] = true;
+  }
+  CUtensorMap tmA, tmB, tmE;
+  ScatterMaps tmS;
+  const uint64_t kc = static_cast<uint64_t>(a.K) / 2;
+  if (!make_map_2d(&tmA, a.values, a.n_out, kc, kc * 2, C::ROWS_CTA, C::BK / 2, CU_TENSOR_MAP_SWIZZLE_128B, a.fmt))
+    return kErrTensorMap;
+  if (!make_map_2d(&tmB, a.x, a.m_tok, a.K, static_cast<uint64_t>(a.ldx) * 2, C::HALF_N, 64,
+                   CU_TENSOR_MAP_SWIZZLE_128B, a.fmt))
+    return kErrTensorMap;
+  if (!make_map_1d_u64(&tmE, a.meta, meta_bytes(a.n_out, a.K) / 8, 256)) return kErrTensorMap;
+  for (int o = 0; o < 8; ++o) {
+    void* base = peer_slots[o < tp ? o : 0];
+    if (!base || (reinterpret_cast<uintptr_t>(base) & 15)) return kErrInvalid;
+    if (!make_map_2d(&tmS.m[o], base, tok_per_owner, a.n_out, static_cast<uint64_t>(a.n_out) * 2, 16,
+                     C::D_ROW_BYTES / 2, CU_TENSOR_MAP_SWIZZLE_NONE, a.fmt))
+      return kErrTensorMap;
+  }
+  PairParams p;
+  p.bias = a.bias;
+  p.y = nullptr;
+  p.status = a.status;
+  p.n_out = a.n_out;
+  p.m_tok = a.m_tok;
+  p.K = a.K;
+  p.ldy = a.n_out;
+  p.num_m_blks = (a.n_out + C::ROWS_TILE - 1) / C::ROWS_TILE;
+  p.num_n_blks = (a.m_tok + C::BN - 1) / C::BN;
+  p.k_tiles128 = (a.K + 127) / 128;
+  p.fmt = a.fmt;
+  p.act = a.act;
+  p.tok_per_owner = tok_per_owner;
+  const int tiles = p.num_m_blks * p.num_n_blks;
+  int pairs = a.num_sms / 2;
+  if (pairs > tiles) pairs = tiles;
+  if (pairs < 1) pairs = 1;
+  sparse_gemm_pair_scatter_kernel<C><<<2 * pairs, C::THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmE, tmS, p);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
+}
 
 int launch_sparse_gemm_pair(const SparseGemmArgs& a, cudaStream_t stream) {
   if (a.K % 64 != 0 || a.K <= 0 || a.m_tok <= 0 || a.n_out <= 0) return kErrInvalid;

@@ -7,6 +7,14 @@ multiples of 4, so pruning a shard equals sharding the pruned matrix.  Each rank
 out_r[M, H]; their sum (NCCL all-reduce over NVLink) is the FFN output.  Shards whose width is not
 a multiple of 64 are zero-padded (zero gate/up rows give hidden == 0, zero down columns add 0).
 
+Two implementations of the exchange step:
+* ``TensorParallelFFN``: down GEMM, then NCCL all-reduce (the baseline);
+* ``FusedTensorParallelFFN``: the down GEMM's epilogue TMA-stores each partial token block straight
+  into the owning rank's receive slot over NVLink (reduce-scatter fused into the GEMM), then one
+  kernel sums the slots in fp32 and writes the finished block into every rank's output (all-gather
+  fused into the reduction).  Buffers are torch symmetric memory; ranks are ordered by its
+  stream-ordered barrier between the two kernels, so no kernel ever waits on another GPU.
+
 One process per GPU; torch.distributed carries the collective.  With ``chunks > 1`` the token
 dimension is split and the all-reduce of chunk i overlaps the GEMMs of chunk i+1 on a second stream.
 """
@@ -105,3 +113,66 @@ class TensorParallelFFN:
                 dist.all_reduce(out[lo:hi], group=self.group)
         main.wait_stream(self.comm_stream)
         return out
+
+
+class FusedTensorParallelFFN:
+    """TP FFN whose exchange step is fused into the kernels (peer stores over NVLink)."""
+
+    def __init__(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, max_tokens: int, group=None,
+                 down_bias: Optional[torch.Tensor] = None):
+        import ctypes as C
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _lib, ops
+        self.C, self.ops, self.L = C, ops, _lib.lib()
+        self.group = group if group is not None else dist.group.WORLD
+        self.tp = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if not 2 <= self.tp <= 8:
+            raise ValueError("fused tensor-parallel FFN needs 2..8 ranks")
+        self.I, self.H = gate.shape
+        g, u, d = shard_ffn_weights(gate, up, down, self.tp, self.rank)
+        self.Ip = g.shape[0]
+        self.gu = ops.compress_gate_up(g, u)
+        self.dn = ops.compress_weight(d)
+        self.down_bias = down_bias
+        self.dtype = gate.dtype
+        dev = gate.device
+        self.tok_per_owner = -(-(-(-max_tokens // self.tp)) // 16) * 16
+        self.max_tokens = max_tokens
+        Mo, H = self.tok_per_owner, self.H
+        # receive slots [source rank][tok_per_owner, H] and the replicated output [tp * tok_per_owner, H]
+        self.recv = symm_mem.empty((self.tp, Mo, H), dtype=self.dtype, device=dev)
+        self.out = symm_mem.empty((self.tp * Mo, H), dtype=self.dtype, device=dev)
+        self.h_recv = symm_mem.rendezvous(self.recv, self.group)
+        self.h_out = symm_mem.rendezvous(self.out, self.group)
+        blk = Mo * H * self.recv.element_size()
+        VP = C.c_void_p * 8
+        recv_ptrs = [int(p) for p in self.h_recv.buffer_ptrs]
+        out_ptrs = [int(p) for p in self.h_out.buffer_ptrs]
+        # rank o's slot for my partial sums; rank d's output rows of my token block
+        self.peer_slots = VP(*[(recv_ptrs[o] + self.rank * blk) if o < self.tp else None for o in range(8)])
+        self.peer_out = VP(*[(out_ptrs[d] + self.rank * blk) if d < self.tp else None for d in range(8)])
+        self.hidden = torch.empty((max_tokens, self.Ip), dtype=self.dtype, device=dev)
+        self.kernel_launches = 0
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        from . import _lib
+        ops, L, C = self.ops, self.L, self.C
+        M = x.shape[0]
+        if M > self.max_tokens:
+            raise ValueError(f"{M} tokens exceed the {self.max_tokens} this instance was built for")
+        st = torch.cuda.current_stream().cuda_stream
+        dt = ops._dt(x)
+        hidden = self.hidden[:M]
+        ops.sparse_gemm_swiglu(x, self.gu, out=hidden)
+        _lib.check("sfb200_sparse_gemm_scatter", L.sfb200_sparse_gemm_scatter(
+            hidden.data_ptr(), hidden.stride(0), self.dn.values.data_ptr(), self.dn.meta.data_ptr(),
+            C.cast(self.peer_slots, C.POINTER(C.c_void_p)), self.tp, self.tok_per_owner, M, self.H, self.Ip, dt, st))
+        self.h_recv.barrier(channel=0)            # every rank's partial sums have landed
+        bias = self.down_bias.data_ptr() if self.down_bias is not None else None
+        _lib.check("sfb200_reduce_allgather", L.sfb200_reduce_allgather(
+            self.recv.data_ptr(), self.tp, self.tok_per_owner, self.H,
+            C.cast(self.peer_out, C.POINTER(C.c_void_p)), dt, bias, st))
+        self.h_out.barrier(channel=0)             # every rank's finished block has landed everywhere
+        self.kernel_launches += 3
+        return self.out[:M]
