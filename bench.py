@@ -249,6 +249,8 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"      # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     H, I, M = WORKLOADS[args.workload]
@@ -312,6 +314,8 @@ def main():
     barrier()
     ops.device_status()
 
+    timed_step = run_step
+
     # ---- timed region: K steps; per-step events also bracket the gate|up kernel for the roofline
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -320,6 +324,7 @@ def main():
     barrier()
     s0 = torch.cuda.Event(enable_timing=True); s1 = torch.cuda.Event(enable_timing=True)
     s0.record()
+    host_t0 = time.perf_counter()
     if world == 1 and args.chunks == 1:
         for k in range(args.steps):
             ev[k][0].record()
@@ -330,7 +335,8 @@ def main():
             ffn.kernel_launches += 2
     else:
         for k in range(args.steps):
-            run_step()
+            timed_step()
+    host_enqueue_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps
     s1.record()
     barrier()
     clocks = sampler.stop()
@@ -390,7 +396,7 @@ def main():
         e0.record()
         for _ in range(args.steps):
             x.copy_(x_host, non_blocking=True)
-            res = run_step()
+            res = timed_step()
             if rank == 0:
                 out_host.copy_(res, non_blocking=True)
             torch.cuda.current_stream().synchronize()
@@ -451,7 +457,7 @@ def main():
                        "hidden": H, "intermediate": I, "tokens": M,
                        "parallelism": "single GPU" if world == 1 else f"tp{world}: column-parallel gate/up, row-parallel down; {tp_mode}",
                        "l2": "no flush: per-step working set (weights 152 MB + activations 157 MB for the default workload) exceeds the 126 MB L2"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "host_enqueue_ms_per_step": host_enqueue_ms,
             "roofline": roof, "cpu_baseline": cpu, "dense_cublas": dense,
             "prune_compress": {"ms": prune_ms, "gbs": prune_gbs, "frac_of_hbm": prune_gbs / hbm,
                                "what": f"down weight {H}x{I}, 3.125 B/element algorithmic"},
