@@ -27,6 +27,7 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+_REAL_STDOUT = 1
 
 WORKLOADS = {
     # name: (hidden, intermediate, tokens)
@@ -223,12 +224,23 @@ def run_reference_arm(args):
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 # ------------------------------------------------------------------------------------------------
+def emit(line: dict) -> None:
+    """Write the one JSON line to the process's ORIGINAL stdout."""
+    os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
+
+
 def main():
     args = parse_args()
+    # Libraries (NCCL's version banner, for one) print to file descriptor 1.  Point fd 1 at stderr for
+    # the rest of the run and keep the original for the JSON line, so stdout carries exactly one line.
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference_arm(args)
         return
@@ -249,8 +261,6 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"      # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     H, I, M = WORKLOADS[args.workload]
@@ -462,7 +472,7 @@ def main():
             "prune_compress": {"ms": prune_ms, "gbs": prune_gbs, "frac_of_hbm": prune_gbs / hbm,
                                "what": f"down weight {H}x{I}, 3.125 B/element algorithmic"},
         }
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
