@@ -667,6 +667,7 @@ int dispatch_pair(const SparseGemmArgs& a, cudaStream_t stream) {
   if (v == 0) v = pick_pair_variant(a.n_out, a.m_tok, a.K, a.num_sms / 2);
   switch (v) {
     case 1256: return launch_pair_cfg<PairCfg<256, 128, 4, 1, EPI>>(a, stream);
+    case 1257: return launch_pair_cfg<PairCfg<256, 64, 8, 1, EPI>>(a, stream);   // same tile, 64-wide stages
     case 2192: return launch_pair_cfg<PairCfg<192, 64, 6, 2, EPI>>(a, stream);
     case 2208: return launch_pair_cfg<PairCfg<208, 64, 6, 2, EPI>>(a, stream);
     case 2224: return launch_pair_cfg<PairCfg<224, 64, 6, 2, EPI>>(a, stream);

@@ -204,3 +204,45 @@ def test_sparseflow_mlp_module():
             self.down_proj = nn.Linear(I, H, bias=False, device="cuda", dtype=torch.float16)
     assert isinstance(make_sparseflow_mlp(Gated()), SparseFlowMLP)
     assert ops.device_status() == 0
+
+
+def test_model_surgery_replaces_every_mlp():
+    """A two-layer Llama-shaped stack with random weights (no checkpoints exist offline)."""
+    from sparseflow_b200.nn.surgery import replace_llama_mlp_module
+    H, I = 512, 1408
+
+    class MLP(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.gate_proj = nn.Linear(H, I, bias=False, device="cuda", dtype=torch.bfloat16)
+            self.up_proj = nn.Linear(H, I, bias=False, device="cuda", dtype=torch.bfloat16)
+            self.down_proj = nn.Linear(I, H, bias=False, device="cuda", dtype=torch.bfloat16)
+
+        def forward(self, x):
+            return self.down_proj(torch.nn.functional.silu(self.gate_proj(x)) * self.up_proj(x))
+
+    class Layer(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.mlp = MLP()
+
+    class Model(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = nn.ModuleList([Layer(), Layer()])
+
+    torch.manual_seed(0)
+    m = Model()
+    for layer in m.layers:                      # make the weights 2:4 so dense and sparse agree
+        for lin in (layer.mlp.gate_proj, layer.mlp.up_proj, layer.mlp.down_proj):
+            lin.weight.data = ops.prune_compress_24(lin.weight.data, want_values=False, want_meta=False,
+                                                    want_pruned=True)["pruned"]
+    x = torch.randn(2, 64, H, device="cuda", dtype=torch.bfloat16)
+    want = [layer.mlp(x) for layer in m.layers]
+    assert replace_llama_mlp_module(m, SparseFlowPolicy(), down_mode="sparse") == 2
+    for layer, w in zip(m.layers, want):
+        assert isinstance(layer.mlp, SparseFlowMLP)
+        got = layer.mlp(x)
+        err = (got.float() - w.float()).abs().max().item()
+        assert err <= 3e-2 * w.float().pow(2).mean().sqrt().item() + 2.0 ** -8 * w.float().abs().max().item()
+    assert ops.device_status() == 0
