@@ -185,6 +185,35 @@ SFB200_API int sfb200_reduce_allgather(const void* slots, int tp, int rows, int 
 SFB200_API int sfb200_ffn_forward_noalloc(const sfb200_ffn_weights* w, const void* x, int ldx, void* out,
                                           int ldo, int M, void* stream);
 
+/*
+ * Persistent form of one compressed weight (host-only helpers, no GPU work): a 256-byte header
+ * followed by the payload `values | pad to 256 | metadata`, i.e. the block sparseflow_sparse_gemm
+ * takes as Bc.  The reference persists only dense copies and re-runs pruning and
+ * to_sparse_semi_structured at every load (sparseflow/nn/sparseflow_linear.py:60-66); a host that
+ * stores this blob skips both.  `layout_version` names the metadata tile layout: a reader that
+ * gets SFB200_ERROR_NOT_SUPPORTED must re-compress from the dense weight.
+ */
+#define SFB200_BLOB_HEADER_BYTES 256
+#define SFB200_LAYOUT_VERSION 1u
+#define SFB200_BLOB_GATE_UP 1u /* rows are the 16-row interleaved gate|up order */
+#define SFB200_BLOB_TIE_LOW 2u /* pruned with SFB200_TIE_LOW */
+typedef struct {
+  uint32_t layout_version;
+  int32_t dtype, rows, K;
+  uint32_t flags;
+  uint64_t values_offset, values_bytes; /* offsets from the start of the blob */
+  uint64_t meta_offset, meta_bytes;
+  uint64_t total_bytes;
+  uint64_t checksum; /* FNV-1a 64 of the payload, 0 = not recorded */
+} sfb200_blob_info;
+SFB200_API size_t sfb200_blob_bytes(int rows, int K); /* 0 for an unsupported shape */
+SFB200_API uint64_t sfb200_blob_checksum(const void* payload_host, size_t bytes);
+SFB200_API int sfb200_blob_write_header(void* header_host, int rows, int K, int dtype, unsigned flags,
+                                        uint64_t checksum);
+/* Validates magic, version, shape-derived sizes and that `available_bytes` holds the whole blob. */
+SFB200_API int sfb200_blob_read_header(const void* header_host, size_t available_bytes,
+                                       sfb200_blob_info* info);
+
 /* Tuning hook: force the token tile of the tcgen05 kernels on the current device.  0 = automatic;
  * 8 = decode kernel (M <= 32); 32/64/128/192/256 = single-CTA kernel with that token tile; 1256 =
  * CTA-pair kernel, 256-row x 256-token tiles; 2192/2208/2224/2240 = CTA-pair kernel, 512-row tiles

@@ -27,3 +27,6 @@ _safe_export("sparseflow_b200.nn.policy", ["SparseFlowPolicy"])
 _safe_export("sparseflow_b200.nn.sparseflow_linear", ["SparseFlowLinear", "make_sparseflow_linear", "prune_24_dense_weight"])
 _safe_export("sparseflow_b200.nn.sparseflow_mlp", ["SparseFlowMLP", "make_sparseflow_mlp"])
 _safe_export("sparseflow_b200.nn.surgery", ["replace_llama_mlp_module"])
+_safe_export("sparseflow_b200.core", ["compress_2_4", "validate_2_4", "prune_2_4", "sparse_mm", "check_sparse_support",
+                                      "is_sparse_available"])
+_safe_export("sparseflow_b200.nn.sparse_linear", ["SparseLinear"])

@@ -31,6 +31,13 @@ class GpuInfo(C.Structure):
     _fields_ = [("sm_arch", C.c_int32), ("num_sms", C.c_int32), ("shared_mem_kb", C.c_uint64)]
 
 
+class BlobInfo(C.Structure):
+    _fields_ = [("layout_version", C.c_uint32), ("dtype", C.c_int32), ("rows", C.c_int32), ("K", C.c_int32),
+                ("flags", C.c_uint32), ("values_offset", C.c_uint64), ("values_bytes", C.c_uint64),
+                ("meta_offset", C.c_uint64), ("meta_bytes", C.c_uint64), ("total_bytes", C.c_uint64),
+                ("checksum", C.c_uint64)]
+
+
 class SfbError(RuntimeError):
     def __init__(self, fn: str, code: int):
         msg = lib().sfb200_status_string(code).decode()
@@ -69,6 +76,12 @@ def lib() -> C.CDLL:
     L.sfb200_reduce_allgather.argtypes = [vp, i, i, i, C.POINTER(vp), i, vp, vp]
     L.sfb200_ffn_forward_noalloc.argtypes = [C.POINTER(FFNWeights), vp, i, vp, i, i, vp]
     L.sfb200_debug_force_token_tile.argtypes = [i]
+    L.sfb200_blob_bytes.restype = sz
+    L.sfb200_blob_bytes.argtypes = [i, i]
+    L.sfb200_blob_checksum.restype = C.c_uint64
+    L.sfb200_blob_checksum.argtypes = [vp, sz]
+    L.sfb200_blob_write_header.argtypes = [vp, i, i, i, C.c_uint, C.c_uint64]
+    L.sfb200_blob_read_header.argtypes = [vp, sz, C.POINTER(BlobInfo)]
     _lib = L
     return L
 

@@ -58,7 +58,7 @@ const char* sfb200_status_string(int status) {
     case SFB200_ERROR_INVALID_ARGUMENT: return "invalid argument";
     case SFB200_ERROR_OUT_OF_MEMORY: return "out of device memory";
     case SFB200_ERROR_CUDA: return "CUDA error (no usable device, or a launch failed)";
-    case SFB200_ERROR_NOT_SUPPORTED: return "not supported (needs an sm_100 device)";
+    case SFB200_ERROR_NOT_SUPPORTED: return "not supported (device is not sm_100, or a layout version this library does not read)";
     case SFB200_ERROR_TENSOR_MAP: return "TMA tensor map could not be encoded";
     case SFB200_ERROR_DEVICE: return "device-side failure (bounded wait ran out)";
     case SFB200_ERROR_SCRATCH_TOO_SMALL:

@@ -49,6 +49,49 @@ class SparseFlowFusedMLP(nn.Module):
         if ok16 and I % 64 == 0 and H % 8 == 0 and ops.validate_24(self.down_weight):
             self._down_sparse = ops.compress_weight(self.down_weight)
 
+    def compressed_state(self) -> dict:
+        """The packed weights as ``uint8`` blobs (plus the bias): what a checkpoint needs to rebuild the
+        sparse path without pruning, validating or compressing again.  Keys absent = that GEMM is dense."""
+        from . import serialize
+        st = {}
+        gu = self._gate_up_sparse if self._gate_up_sparse is not None else self._gate_up_plain
+        if gu is not None:
+            st["gate_up"] = serialize.pack(gu)
+        if self._down_sparse is not None:
+            st["down"] = serialize.pack(self._down_sparse)
+        if self.down_bias is not None:
+            st["down_bias"] = self.down_bias.detach()
+        return st
+
+    @classmethod
+    def from_compressed_state(cls, state: dict, act_fn=nn.SiLU(), force_mode: str = "sparse") -> "SparseFlowFusedMLP":
+        """Rebuild from ``compressed_state()``.  Both GEMMs must be present in packed form; the module
+        holds no dense weights, so only ``force_mode="sparse"`` is possible."""
+        from . import serialize
+        if force_mode != "sparse":
+            raise ValueError("a module rebuilt from packed weights has no dense copy: force_mode must be 'sparse'")
+        if "gate_up" not in state or "down" not in state:
+            raise ValueError("state needs both 'gate_up' and 'down' blobs")
+        self = cls.__new__(cls)
+        nn.Module.__init__(self)
+        gu, down = serialize.unpack(state["gate_up"]), serialize.unpack(state["down"])
+        if gu.rows != 2 * down.K or gu.K != down.rows:
+            raise ValueError(f"gate_up {gu.rows}x{gu.K} and down {down.rows}x{down.K} do not form a gated FFN")
+        self.act_fn, self.force_mode, self.debug = act_fn, force_mode, False
+        self.hidden_size, self.intermediate_size = gu.K, down.K
+        self._silu = isinstance(act_fn, nn.SiLU) or act_fn is torch.nn.functional.silu
+        if gu.gate_up != self._silu:
+            raise ValueError("the gate|up blob's row order does not match the activation it was packed for")
+        self.fused_gate_up_weight = None
+        self.down_weight = None
+        self.down_bias = state.get("down_bias")
+        self._gate_up_sparse = gu if gu.gate_up else None
+        self._gate_up_plain = None if gu.gate_up else gu
+        self._down_sparse = down
+        self._shape_gu = (gu.rows, gu.K)
+        self._shape_d = (down.rows, down.K)
+        return self
+
     def _has_gu_sparse(self) -> bool:
         return self._gate_up_sparse is not None or self._gate_up_plain is not None
 
@@ -57,8 +100,8 @@ class SparseFlowFusedMLP(nn.Module):
         orig_shape = x.shape
         x_2d = x.reshape(-1, self.hidden_size)
         M_eff = x_2d.shape[0]
-        out_gu, in_gu = self.fused_gate_up_weight.shape
-        out_d, in_d = self.down_weight.shape
+        out_gu, in_gu = self._shape_gu if self.fused_gate_up_weight is None else self.fused_gate_up_weight.shape
+        out_d, in_d = self._shape_d if self.down_weight is None else self.down_weight.shape
 
         use_sparse_gu = self._has_gu_sparse() and (
             self.force_mode == "sparse"

@@ -21,3 +21,4 @@ _safe_export("sparseflow_b200.nn.policy", ["SparseFlowPolicy"])
 _safe_export("sparseflow_b200.nn.surgery", ["replace_llama_mlp_module"])
 _safe_export("sparseflow_b200.nn.sparseflow_linear", ["SparseFlowLinear", "make_sparseflow_linear", "prune_24_dense_weight"])
 _safe_export("sparseflow_b200.nn.sparseflow_mlp", ["SparseFlowMLP", "make_sparseflow_mlp"])
+_safe_export("sparseflow_b200.nn.sparse_linear", ["SparseLinear"])
