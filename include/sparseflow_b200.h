@@ -220,6 +220,13 @@ SFB200_API int sfb200_blob_read_header(const void* header_host, size_t available
  * with that many tokens.  No counterpart upstream. */
 SFB200_API int sfb200_debug_force_token_tile(int bn);
 
+/* Tuning hooks of sfb200_ffn_forward_host's copy/compute pipeline: tokens are processed in chunks
+ * of `main_rows` while more than that remains, then the remainder is halved down to `tail_rows`
+ * (small last chunks shorten what runs after the last host-to-device copy but run the GEMMs less
+ * efficiently).  0 = default (1024 / 1024).  _chunk_plan is host-only and returns the number of chunks written to out8[8]. */
+SFB200_API int sfb200_debug_host_pipeline(int main_rows, int tail_rows);
+SFB200_API int sfb200_debug_host_chunk_plan(int M, int main_rows, int tail_rows, int* out8);
+
 /* ------------------------------------------------------------------ 2. sf_* runtime API --- */
 /* experiments/old_structure/runtime/api/sparseflow_api.h:8-28, exercised by tests/test_c_api.cpp. */
 

@@ -50,6 +50,32 @@ DeviceState* device_state(int* err) {
 
 }  // namespace sfb200
 
+// Token-chunk plan of the host-buffer pipeline; returns the number of chunks (<= kMaxChunks),
+// sizes in out[], multiples of 8 except the last.  main_rows / tail_rows <= 0 select the defaults.
+int plan_host_chunks(int M, int main_rows, int tail_rows, int* out) {
+  constexpr int kMax = DeviceState::kMaxChunks;
+  if (main_rows <= 0) main_rows = 1024;
+  if (tail_rows <= 0) tail_rows = 1024;  // measured on B200 + PCIe 5: halving the tail did not pay (0.976 vs 0.995 ms at 4096 tokens)
+  if (tail_rows > main_rows) tail_rows = main_rows;
+  // at most kMax - 3 main chunks, so the halving tail always has room
+  const int min_main = (M + (kMax - 3) - 1) / (kMax - 3);
+  if (main_rows < min_main) main_rows = min_main;
+  main_rows = (main_rows + 7) & ~7;
+  int n = 0, rem = M;
+  while (rem > main_rows && n < kMax - 3) {
+    out[n++] = main_rows;
+    rem -= main_rows;
+  }
+  while (rem > tail_rows && n < kMax - 1) {
+    int half = ((rem + 1) / 2 + 7) & ~7;
+    if (half >= rem) break;
+    out[n++] = half;
+    rem -= half;
+  }
+  if (rem > 0) out[n++] = rem;
+  return n;
+}
+
 extern "C" {
 
 const char* sfb200_status_string(int status) {
@@ -257,17 +283,19 @@ int sfb200_ffn_forward_host(const sfb200_ffn_weights* w, const void* x_host, voi
       s->pipe_ready = true;
     }
   }
-  int chunks = M / 1024;
-  if (chunks < 1) chunks = 1;
-  if (chunks > DeviceState::kMaxChunks) chunks = DeviceState::kMaxChunks;
-  const int rows_per = ((M + chunks - 1) / chunks + 7) & ~7;
+  // Chunk plan: `main` rows per chunk while more than that remains, then the remainder is halved
+  // down to `tail` rows.  The copy-in stream is the bottleneck (PCIe); what follows the last
+  // copy-in -- FFN and copy-out of the LAST chunk -- is pure latency, but small chunks also run
+  // the GEMMs less efficiently, so the default keeps the tail at the main size.
+  int plan[DeviceState::kMaxChunks];
+  const int n_chunks = plan_host_chunks(M, s->host_main_rows, s->host_tail_rows, plan);
   const size_t row_x = static_cast<size_t>(w->H) * 2, row_h = static_cast<size_t>(w->I) * 2;
   if (cudaEventRecord(s->ev_start, st) != cudaSuccess) return kErrCuda;
   if (cudaStreamWaitEvent(s->s_in, s->ev_start, 0) != cudaSuccess) return kErrCuda;
   if (cudaStreamWaitEvent(s->s_out, s->ev_start, 0) != cudaSuccess) return kErrCuda;
-  int c = 0;
-  for (int r0 = 0; r0 < M; r0 += rows_per, ++c) {
-    const int rows = (M - r0 < rows_per) ? M - r0 : rows_per;
+  int r0 = 0;
+  for (int c = 0; c < n_chunks; r0 += plan[c], ++c) {
+    const int rows = plan[c];
     uint8_t* xd = static_cast<uint8_t*>(s->stage_x) + r0 * row_x;
     uint8_t* od = static_cast<uint8_t*>(s->stage_o) + r0 * row_x;
     uint8_t* hd = static_cast<uint8_t*>(s->stage_h) + r0 * row_h;
@@ -330,6 +358,22 @@ SFB200_API int sfb200_debug_force_token_tile(int bn) {
   DeviceState* s = device_state(&err);
   if (!s) return err;
   s->force_bn = bn;
+  return kOk;
+}
+
+/* The chunk plan sfb200_ffn_forward_host would use for M tokens (host-only; out8 holds 8 ints). */
+SFB200_API int sfb200_debug_host_chunk_plan(int M, int main_rows, int tail_rows, int* out8) {
+  if (M <= 0 || !out8) return 0;
+  return plan_host_chunks(M, main_rows, tail_rows, out8);
+}
+
+/* Tuning hook: rows per main chunk / smallest tail chunk of sfb200_ffn_forward_host (0 = default). */
+SFB200_API int sfb200_debug_host_pipeline(int main_rows, int tail_rows) {
+  int err = kOk;
+  DeviceState* s = device_state(&err);
+  if (!s) return err;
+  s->host_main_rows = main_rows;
+  s->host_tail_rows = tail_rows;
   return kOk;
 }
 

@@ -21,6 +21,7 @@ struct DeviceState {
   size_t stage_h_bytes = 0;
   // host-buffer FFN pipeline: copy-in / copy-out streams and per-chunk events
   static constexpr int kMaxChunks = 8;
+  int host_main_rows = 0, host_tail_rows = 0;  // chunk plan overrides of the host-buffer pipeline (0 = default)
   cudaStream_t s_in = nullptr, s_out = nullptr;
   cudaEvent_t ev_start = nullptr, ev_done = nullptr;
   cudaEvent_t ev_in[kMaxChunks] = {}, ev_cmp[kMaxChunks] = {};

@@ -159,3 +159,21 @@ def test_package_has_no_oracle_dependency():
             if f.endswith((".py", ".cu", ".cpp", ".h", ".cuh")):
                 src = open(os.path.join(dirpath, f)).read()
                 assert not re.search(r"^\s*(import|from)\s+oracle\b", src, re.M), f
+
+
+def test_host_pipeline_chunk_plan_covers_every_token():
+    """Chunks are multiples of 8 rows (16-byte aligned row offsets for TMA) except the last, at most 8,
+    and sum to M for any M and any tuning override."""
+    import ctypes as C
+    from sparseflow_b200 import _lib
+    L = _lib.lib()
+    out = (C.c_int * 8)()
+    for M in (1, 7, 8, 511, 512, 1000, 1024, 1025, 4096, 5000, 16384, 100000, 1 << 20):
+        for main, tail in ((0, 0), (1024, 256), (2048, 512), (512, 128), (64, 8), (4096, 4096)):
+            n = L.sfb200_debug_host_chunk_plan(M, main, tail, out)
+            plan = list(out[:n])
+            assert 1 <= n <= 8 and sum(plan) == M and min(plan) > 0, (M, main, tail, plan)
+            assert all(r % 8 == 0 for r in plan[:-1]), (M, main, tail, plan)
+    n = L.sfb200_debug_host_chunk_plan(4096, 0, 0, out)
+    assert list(out[:n]) == [1024] * 4
+    assert L.sfb200_debug_host_chunk_plan(0, 0, 0, out) == 0 and L.sfb200_debug_host_chunk_plan(8, 0, 0, None) == 0
