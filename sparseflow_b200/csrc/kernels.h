@@ -80,6 +80,13 @@ int launch_sparse_gemm_pair_scatter(const SparseGemmArgs& a, void* const* peer_s
 int launch_reduce_allgather(const void* slots, int tp, int rows, int cols, void* const* peer_out_blocks, int fmt,
                             const void* bias, cudaStream_t stream);
 
+// Split-K variant of the single-CTA kernel: a cluster of `split` (2 or 4) CTAs shares one output tile,
+// each streaming a slice of K; partial tiles are reduced through distributed shared memory.  Chosen by
+// launch_sparse_gemm when splitk_factor() > 1 (too few row tiles to occupy the SMs).  kEpiStore only.
+int launch_sparse_gemm_splitk(const SparseGemmArgs& a, int split, cudaStream_t stream);
+int splitk_factor(int m_tok, int n_out, int K, int num_sms);
+int splitk_token_tile(int m_tok);
+
 // ---- small-M (decode) sparse GEMM ----------------------------------------------------------
 // M <= 32 tokens; chosen by launch_sparse_gemm for m_tok <= kSmallMMaxTokens (force_bn == 8 forces it).
 int launch_sparse_gemm_small_m(const SparseGemmArgs& a, cudaStream_t stream);

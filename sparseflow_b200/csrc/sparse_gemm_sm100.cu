@@ -381,11 +381,20 @@ int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream) {
   if ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.values) |
        reinterpret_cast<uintptr_t>(a.meta) | reinterpret_cast<uintptr_t>(a.y)) & 15)
     return kErrInvalid;
-  // decode-sized token counts: bandwidth kernel on warp-level mma.sp (force with 8, avoid with any other tile)
-  if (a.force_bn == 8 || (a.force_bn == 0 && a.m_tok <= kSmallMMaxTokens)) return launch_sparse_gemm_small_m(a, stream);
+  // few row tiles (the weight has fewer 128-row tiles than half the SMs) and fewer tokens than the
+  // prefill kernel wants: split K over a cluster so that the weight is streamed by (nearly) every SM
+  const int split = (a.force_bn == 0 && a.epi == kEpiStore && a.m_tok < kPairMinTokens)
+                        ? splitk_factor(a.m_tok, a.n_out, a.K, a.num_sms) : 1;
+  // decode-sized token counts: bandwidth kernel on warp-level mma.sp (force with 8, avoid with any other
+  // tile); measured against the split-K kernel it only wins at 1-2 tokens when both apply
+  if (a.force_bn == 8 || (a.force_bn == 0 && a.m_tok <= kSmallMMaxTokens && (split == 1 || a.m_tok <= 2)))
+    return launch_sparse_gemm_small_m(a, stream);
   // CTA-pair kernel for prefill-sized token counts (or when forced: 1256, 2192..2240)
-  if (a.force_bn >= 1000 || (a.force_bn == 0 && a.m_tok >= kPairMinTokens))
+  if ((a.force_bn >= 1000 && a.force_bn < 3000) || (a.force_bn == 0 && a.m_tok >= kPairMinTokens))
     return launch_sparse_gemm_pair(a, stream);
+  // forced split-K: 3000 + token tile for 2 slices, 4000 + token tile for 4
+  if (a.force_bn >= 3000) return launch_sparse_gemm_splitk(a, a.force_bn >= 4000 ? 4 : 2, stream);
+  if (split > 1) return launch_sparse_gemm_splitk(a, split, stream);
   if (a.epi == kEpiSwiGLU) {
     if (a.n_out % 32 != 0 || (a.n_out / 2) % 8 != 0) return kErrInvalid;
     return dispatch_bn<kEpiSwiGLU>(a, stream);

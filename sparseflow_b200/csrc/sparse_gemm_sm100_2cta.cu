@@ -32,20 +32,6 @@ namespace sfb200 {
 namespace {
 
 // ---------------------------------------------------------------- cluster / pair PTX
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::
-                   : "memory");
-}
-__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
 // Arrive on a barrier of the pair's even CTA.  Default semantics (release at CTA scope) on purpose:
 // a cluster-scope release would hold the arrive back until this thread's global stores of the
 // previous tile have reached L2, and the arrive only has to order tensor-memory reads, which

@@ -96,6 +96,53 @@ def test_bias_and_activation_epilogues(bn, act):
     assert o.rel_err_metrics(y, ref)["floor"] <= REL_TOL
 
 
+# ---- split-K over a cluster (3000 + token tile = 2 K-slices, 4000 + token tile = 4 K-slices)
+@pytest.mark.parametrize("bn,M", [(3032, 20), (3064, 40), (3128, 100), (4032, 32), (4064, 64), (4128, 128),
+                                  (4128, 300)])
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+def test_split_k_variants_ragged(bn, M, dt):
+    """Rows not a multiple of 128, K with a 64-wide tail (9 metadata tiles split 3/2/2/2), ragged tokens."""
+    y, ref = _run(392, 1024 + 64, M, dt, bn=bn)
+    assert y.shape == (M, 392)
+    assert o.rel_err_metrics(y, ref)["floor"] <= REL_TOL
+
+
+@pytest.mark.parametrize("bn", [3064, 4128])
+def test_split_k_identity_is_exact(bn):
+    dt, R, K, M = "bf16", 256, 1024, 128
+    w = seeded_weight(R, K, dt, 3)
+    cw = ops.compress_weight(to_dev(w, dt))
+    x = o.from_f32(np.eye(M, K, dtype=np.float32), dt)
+    ops.force_token_tile(bn)
+    y = ops.sparse_gemm(to_dev(x, dt), cw)
+    assert ops.device_status() == 0
+    assert (bits_of(y).T == o.prune_24(w, dt)["pruned"][:, :M]).all()
+
+
+@pytest.mark.parametrize("act", [None, "relu", "silu", "gelu"])
+def test_split_k_bias_and_activation(act):
+    y, ref = _run(256, 2048, 96, "f16", bn=4128, bias=True, act=act)
+    assert o.rel_err_metrics(y, ref)["floor"] <= REL_TOL
+
+
+@pytest.mark.parametrize("R,K,M", [(4096, 11008, 16), (4096, 11008, 128), (4096, 4096, 64), (4096, 14336, 256),
+                                   (8192, 8192, 32)])
+def test_split_k_auto_dispatch_on_few_row_tiles(R, K, M):
+    """Shapes the dispatcher sends to the split-K kernel (32 or 64 row tiles on 148 SMs); the result is
+    also bit-identical from one launch to the next (fixed summation order, no atomics)."""
+    dt = "bf16"
+    w = seeded_weight(R, K, dt, 6)
+    x = seeded_act(M, K, dt, 7)
+    cw = ops.compress_weight(to_dev(w, dt))
+    xd = to_dev(x, dt)
+    y1 = ops.sparse_gemm(xd, cw)
+    y2 = ops.sparse_gemm(xd, cw)
+    assert ops.device_status() == 0
+    assert torch.equal(y1, y2)
+    ref = o.gemm_ref(x, o.prune_24_pruned_chunked(w, dt), dt)
+    assert o.rel_err_metrics(o.to_f32(bits_of(y1), dt), ref)["floor"] <= REL_TOL
+
+
 def test_config1_fp16_m512_k4096_n4096():
     y, ref = _run(4096, 4096, 512, "f16", wseed=1, xseed=1234)
     m = o.rel_err_metrics(y, ref)
