@@ -214,10 +214,11 @@ SFB200_API int sfb200_blob_write_header(void* header_host, int rows, int K, int 
 SFB200_API int sfb200_blob_read_header(const void* header_host, size_t available_bytes,
                                        sfb200_blob_info* info);
 
-/* Tuning hook: force the token tile of the tcgen05 kernels on the current device.  0 = automatic;
+/* Tuning hook: force the kernel variant / token tile on the current device.  0 = automatic;
  * 8 = decode kernel (M <= 32); 32/64/128/192/256 = single-CTA kernel with that token tile; 1256 =
  * CTA-pair kernel, 256-row x 256-token tiles; 2192/2208/2224/2240 = CTA-pair kernel, 512-row tiles
- * with that many tokens.  No counterpart upstream. */
+ * with that many tokens; 3032/3064/3128 and 4032/4064/4128 = split-K cluster kernel with 2 or 4
+ * K slices and a 32/64/128-token tile.  No counterpart upstream. */
 SFB200_API int sfb200_debug_force_token_tile(int bn);
 
 /* Tuning hooks of sfb200_ffn_forward_host's copy/compute pipeline: tokens are processed in chunks

@@ -314,6 +314,7 @@ int splitk_factor(int m_tok, int n_out, int K, int num_sms) {
   if (tiles * 4 <= num_sms) s = 4;
   else if (tiles * 2 <= num_sms) s = 2;
   while (s > 1 && k128 < 4 * s) s >>= 1;   // at least four metadata tiles (K = 512) per slice
+  if (bn == 128 && s == 2) s = 1;          // measured: two slices of a 128-token tile gain nothing (X traffic dominates)
   return s;
 }
 

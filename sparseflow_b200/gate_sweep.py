@@ -6,6 +6,8 @@ Per projection class (the classes of ``dispatch.classify_projection``) and token
 sparse path of this library against the dense library GEMM on the same 2:4-pruned weight stored
 dense (the reference's "pruned-dense" baseline, tools/bench_mlp_mistral.py:50-53), CUDA events,
 rotating over several weight copies so small-M timings stream weights from HBM rather than L2.
+Token counts up to 512 are timed as a CUDA graph of 20 launches (device time; the eager figures, which
+include host enqueue cost, are recorded beside them).
 Decision rule as in the reference's override generator
 (tools/make_shape_overrides_sm89_from_results.py:18-22,99-127): sparse iff speed-up >= min_speedup.
 ``min_m`` = smallest measured M from which every larger M is a sparse win; ``decode_max_m`` = largest
@@ -42,6 +44,32 @@ def _time(fn, iters):
     return e0.elapsed_time(e1) / iters
 
 
+def _time_graph(fn, launches=20, replays=5):
+    """Device time per launch: `launches` calls captured in one CUDA graph (each call rotates to the
+    next weight copy), replayed `replays` times.  Host enqueue cost, which dominates eager timings of
+    kernels shorter than ~15 us, is excluded."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(launches):
+            fn()
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (launches * replays)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=os.path.join(os.path.dirname(os.path.abspath(__file__)), "gate_sm100.json"))
@@ -72,9 +100,18 @@ def main():
                     torch.matmul(x, wd[i[0] % copies].t(), out=y)
                     i[0] += 1
                 ts, td = _time(fs, iters), _time(fd, iters)
-                rows.append({"class": cls, "K": K, "N": N, "M": M, "sparse_us": ts * 1e3, "dense_us": td * 1e3,
-                             "speedup": td / ts, "sparse_tflops": 2.0 * M * N * K / ts / 1e9})
-                print(f"{cls:12s} K={K:6d} N={N:6d} M={M:5d} sparse {ts*1e3:8.1f} us dense {td*1e3:8.1f} us  x{td/ts:.2f}", flush=True)
+                row = {"class": cls, "K": K, "N": N, "M": M, "eager_sparse_us": ts * 1e3, "eager_dense_us": td * 1e3}
+                if M <= 512:      # short kernels: decide on device time, not on host enqueue time
+                    ts, td = _time_graph(fs), _time_graph(fd)
+                    row["timing"] = "cuda graph of 20 launches"
+                else:
+                    row["timing"] = "eager, CUDA events"
+                row.update({"sparse_us": ts * 1e3, "dense_us": td * 1e3, "speedup": td / ts,
+                            "sparse_tflops": 2.0 * M * N * K / ts / 1e9,
+                            "sparse_gbs": (N * K * 1.125 + M * K * 2 + M * N * 2) / ts / 1e6})
+                rows.append(row)
+                print(f"{cls:12s} K={K:6d} N={N:6d} M={M:5d} sparse {ts*1e3:8.1f} us dense {td*1e3:8.1f} us  x{td/ts:.2f}"
+                      f"   (eager {row['eager_sparse_us']:.1f} / {row['eager_dense_us']:.1f})", flush=True)
             del ws, wd
     ops.device_status()
     table = {"min_m": {}, "max_m": {}, "decode_max_m": {}}
@@ -94,9 +131,8 @@ def main():
                 dec = M
             else:
                 break
-        if min_m is not None and dec >= min_m:
-            dec = 0 if min_m > 1 else dec      # one contiguous band: expressed through min_m alone
-            min_m = 1 if win[TOKENS[0]] and all(win.values()) else min_m
+        if all(win.values()):                  # one band covering everything
+            min_m, dec = 1, 0
         table["min_m"][cls] = min_m if min_m is not None else 1 << 30
         table["max_m"][cls] = 1 << 20
         table["decode_max_m"][cls] = dec

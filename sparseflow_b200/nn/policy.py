@@ -3,8 +3,20 @@
 Same dataclass and methods as the reference's ``sparseflow/nn/policy.py`` (fields :13-27,
 ``load_runtime_policy`` :37-72, ``should_use_sparse`` :74-95), including its substring matching of
 ``op_name.lower()`` (any name containing "gate" or "up" is a gate/up op, and so on).  Defaults are
-B200 numbers instead of the reference's A100 ones."""
-from dataclasses import dataclass
+the B200 crossovers of the measured gate table (``gate_sm100.json``, see ``dispatch.py``) instead of
+the reference's A100 numbers, and each op class has a second, low band ``M <= decode_max_M_*`` in which
+the sparse path wins because it streams 0.5625x the weight bytes (0 = no such band)."""
+from dataclasses import dataclass, field
+
+from .. import dispatch as _gate
+
+
+def _lo(cls):
+    return field(default_factory=lambda: int(_gate.THRESHOLDS[cls]))
+
+
+def _dec(cls):
+    return field(default_factory=lambda: int(_gate.DECODE_MAX_M[cls]))
 
 
 @dataclass
@@ -12,12 +24,18 @@ class SparseFlowPolicy:
     min_M_default: int = 1024
 
     # MLP thresholds (B200 crossovers against cuBLAS on the same pruned weights)
-    min_M_gate_up: int = 512
-    min_M_down: int = 1024
+    min_M_gate_up: int = _lo("ffn_gate_up")
+    min_M_down: int = _lo("ffn_down")
 
     # Attention projections
-    min_M_qkv: int = 1024
-    min_M_o: int = 1024
+    min_M_qkv: int = _lo("attn_proj")
+    min_M_o: int = _lo("attn_proj")
+
+    # Low (bandwidth-bound) band, not present upstream
+    decode_max_M_gate_up: int = _dec("ffn_gate_up")
+    decode_max_M_down: int = _dec("ffn_down")
+    decode_max_M_qkv: int = _dec("attn_proj")
+    decode_max_M_o: int = _dec("attn_proj")
 
     # Upper bounds: none observed on B200 up to M = 16384
     max_M_gate_up: int = 1 << 20
@@ -76,11 +94,11 @@ class SparseFlowPolicy:
             return False
         op_lower = op_name.lower()
         if "gate" in op_lower or "up" in op_lower:
-            return self.min_M_gate_up <= M <= self.max_M_gate_up
+            return M <= self.decode_max_M_gate_up or self.min_M_gate_up <= M <= self.max_M_gate_up
         if "down" in op_lower:
-            return self.min_M_down <= M <= self.max_M_down
+            return M <= self.decode_max_M_down or self.min_M_down <= M <= self.max_M_down
         if any(x in op_lower for x in ["q_proj", "k_proj", "v_proj"]):
-            return self.min_M_qkv <= M <= self.max_M_qkv
+            return M <= self.decode_max_M_qkv or self.min_M_qkv <= M <= self.max_M_qkv
         if "o_proj" in op_lower or "o" == op_lower:
-            return self.min_M_o <= M <= self.max_M_o
+            return M <= self.decode_max_M_o or self.min_M_o <= M <= self.max_M_o
         return M >= self.min_M_default

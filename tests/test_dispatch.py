@@ -58,3 +58,15 @@ def test_policy_substring_semantics_and_json(tmp_path):
                                        "q_proj": {"max_m": 999}, "o_proj": {"min_m": 7}, "note": "x"}}))
     pol.load_runtime_policy(str(p))
     assert (pol.min_M_gate_up, pol.max_M_gate_up, pol.min_M_down, pol.max_M_qkv, pol.min_M_o) == (128, 16384, 640, 999, 7)
+
+
+def test_policy_low_band_and_defaults_follow_the_measured_table():
+    pol = SparseFlowPolicy()
+    assert pol.min_M_gate_up == dispatch.THRESHOLDS["ffn_gate_up"] and pol.min_M_down == dispatch.THRESHOLDS["ffn_down"]
+    assert pol.min_M_qkv == pol.min_M_o == dispatch.THRESHOLDS["attn_proj"]
+    assert pol.decode_max_M_down == dispatch.DECODE_MAX_M["ffn_down"]
+    pol = SparseFlowPolicy(min_M_down=512, decode_max_M_down=64, min_M_qkv=2048, decode_max_M_qkv=0)
+    assert pol.should_use_sparse("down_proj", 1) and pol.should_use_sparse("down_proj", 64)
+    assert not pol.should_use_sparse("down_proj", 65) and not pol.should_use_sparse("down_proj", 511)
+    assert pol.should_use_sparse("down_proj", 512)
+    assert not pol.should_use_sparse("k_proj", 1) and pol.should_use_sparse("k_proj", 2048)
