@@ -131,7 +131,35 @@ struct PairParams {
   int k_tiles128;
   int fmt, act;
   int tok_per_owner;   // scatter epilogue: tokens owned by each rank (0 = plain output)
+  int band;            // token tiles per L2 band (see tile_coords)
 };
+
+// Tile order.  Tiles are walked band by band: a band is `band` consecutive token tiles, and inside a
+// band the row tile is the slow index.  The SM pairs working at the same time therefore share one or
+// two weight tiles and one band of activations; the band is sized so that its activations stay in
+// L2 while every row tile passes over them.  Without bands, a token operand larger than L2 (16384
+// tokens x 4096, 8192 x 8192) is re-read from HBM once per row tile and the GEMM becomes HBM-bound.
+__device__ __forceinline__ void tile_coords(int tile, const PairParams& p, int& m_blk, int& n_blk) {
+  const int per_band = p.num_m_blks * p.band;
+  const int b = tile / per_band;
+  const int r = tile - b * per_band;
+  const int left = p.num_n_blks - b * p.band;
+  const int width = left < p.band ? left : p.band;
+  m_blk = r / width;
+  n_blk = b * p.band + (r - m_blk * width);
+}
+
+// Token tiles per band: activations of a band (tokens x K x 2 bytes) within ~40 MB of the 126 MB L2.
+inline int pick_band(int bn, int K, int num_n_blks) {
+  const long per_blk = static_cast<long>(bn) * K * 2;
+  long band = (40l << 20) / (per_blk > 0 ? per_blk : 1);
+  if (band < 1) band = 1;
+  if (band >= num_n_blks) return num_n_blks;
+  // equal-width bands: avoid a narrow last band
+  const long nb = (num_n_blks + band - 1) / band;
+  band = (num_n_blks + nb - 1) / nb;
+  return static_cast<int>(band);
+}
 
 // Output tensor maps of the scatter epilogue: one per destination rank (its receive slot for this
 // rank's partial sums, mapped into this GPU's address space).
@@ -337,8 +365,8 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
       uint32_t ph = 0;
       bool ok = true;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
-        const int m_blk = tile / p.num_n_blks;
-        const int n_blk = tile % p.num_n_blks;
+        int m_blk, n_blk;
+        tile_coords(tile, p, m_blk, n_blk);
         const int row0 = m_blk * C::ROWS_TILE + static_cast<int>(rank) * C::ROWS_CTA;
         const int tok0 = n_blk * C::BN + static_cast<int>(rank) * C::HALF_N;
         const int e_rt0 = row0 >> 7;   // first 128-row metadata tile of this CTA
@@ -432,8 +460,8 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
     constexpr int NCH = C::COLS_PER_WARP / 16;
     const bool upper = lane >= 16;
     for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
-      const int m_blk = tile / p.num_n_blks;
-      const int n_blk = tile % p.num_n_blks;
+      int m_blk, n_blk;
+      tile_coords(tile, p, m_blk, n_blk);
       {
         bool w = mbar_wait(bar_accf, aph, err, p.status, 4);
         ok = __all_sync(0xffffffffu, w);
@@ -615,6 +643,7 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
   p.fmt = a.fmt;
   p.act = a.act;
   p.tok_per_owner = 0;
+  p.band = pick_band(C::BN, a.K, p.num_n_blks);
   const int tiles = p.num_m_blks * p.num_n_blks;
   int pairs = a.num_sms / 2;
   if (pairs > tiles) pairs = tiles;
@@ -709,6 +738,7 @@ int launch_sparse_gemm_pair_scatter(const SparseGemmArgs& a, void* const* peer_s
   p.fmt = a.fmt;
   p.act = a.act;
   p.tok_per_owner = tok_per_owner;
+  p.band = pick_band(C::BN, a.K, p.num_n_blks);
   const int tiles = p.num_m_blks * p.num_n_blks;
   int pairs = a.num_sms / 2;
   if (pairs > tiles) pairs = tiles;

@@ -143,6 +143,15 @@ def test_split_k_auto_dispatch_on_few_row_tiles(R, K, M):
     assert o.rel_err_metrics(o.to_f32(bits_of(y1), dt), ref)["floor"] <= REL_TOL
 
 
+@pytest.mark.parametrize("bn", [0, 2240])
+def test_pair_kernel_l2_band_tile_order(bn):
+    """Enough token tiles at K = 8192 that the prefill kernel walks them in more than one L2 band
+    (12-13 token tiles, bands of 6-7), with ragged rows and tokens."""
+    y, ref = _run(520, 8192, 3000, "bf16", bn=bn)
+    assert y.shape == (3000, 520)
+    assert o.rel_err_metrics(y, ref)["floor"] <= REL_TOL
+
+
 def test_config1_fp16_m512_k4096_n4096():
     y, ref = _run(4096, 4096, 512, "f16", wseed=1, xseed=1234)
     m = o.rel_err_metrics(y, ref)
