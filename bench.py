@@ -233,6 +233,13 @@ def emit(line: dict) -> None:
     os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
 
 
+def _p50_p95(xs):
+    """Median and 95th percentile of per-step device times (the reference's demo reports these two,
+    demo/demo_harness.py:90-102)."""
+    xs = sorted(xs)
+    return [xs[len(xs) // 2], xs[min(len(xs) - 1, int(round(0.95 * (len(xs) - 1))))]]
+
+
 def main():
     args = parse_args()
     # Libraries (NCCL's version banner, for one) print to file descriptor 1.  Point fd 1 at stderr for
@@ -375,6 +382,7 @@ def main():
                 "peak_source": f"2 x bf16_tflops ({src}); of {'measured' if src == 'measured' else 'fallback'}",
                 "frac_of_sustained": achieved / (2.0 * sustained),
                 "ms_per_launch": gu_ms,
+                "step_ms_p50_p95": _p50_p95([e[0].elapsed_time(e[2]) for e in ev]),
                 "down_kernel": {"ms_per_launch": dn_ms, "achieved": 2.0 * M * H * I / (dn_ms * 1e-3) / 1e12}}
 
     # ---- end to end through the host-buffer C-ABI call (H2D of x, FFN, D2H of out, every step)
