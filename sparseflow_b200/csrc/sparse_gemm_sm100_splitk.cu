@@ -118,7 +118,9 @@ sparse_gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  cluster_sync_all();   // every CTA of the cluster is resident before anyone stores into a peer's slots
+  // First cluster barrier, split: arrive now, wait only before the first store into a peer's slots
+  // (its purpose is that every CTA of the cluster is resident by then), so the K loop does not pay for it.
+  cluster_arrive();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -184,6 +186,8 @@ sparse_gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     const bool have = kt_end > kt_begin;
     bool ok = true;
     if (have) ok = mbar_wait(bar_accf, 0, err, p.status, 4);
+    __syncwarp();
+    cluster_wait();
     if (ok) {
       tc_fence_after();
       // slot[src rank][token][feature in owner], fp32
@@ -206,6 +210,7 @@ sparse_gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
   }
 
   __syncwarp();
+  if (warp < 2) cluster_wait();   // producer and MMA warps: second half of the first barrier
   tc_fence_before();
   cluster_sync_all();   // all partials have landed in their owners' shared memory
 

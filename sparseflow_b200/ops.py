@@ -165,6 +165,8 @@ def sparse_gemm(x: torch.Tensor, cw: Compressed24, bias: Optional[torch.Tensor] 
     with torch.cuda.device(x.device):
         if out is None:
             out = torch.empty((M, cw.rows), dtype=x.dtype, device=x.device)
+        if M == 0:                      # empty batch: nothing to launch
+            return out
         rc = _lib.lib().sfb200_sparse_gemm(x.data_ptr(), x.stride(0), cw.values.data_ptr(),
                                            cw.meta.data_ptr(), out.data_ptr(), out.stride(0), M, cw.rows,
                                            cw.K, _dt(x), _ptr(bias), ACT[act], _stream())
@@ -185,6 +187,8 @@ def sparse_gemm_swiglu(x: torch.Tensor, cw_gu: Compressed24, out: Optional[torch
     with torch.cuda.device(x.device):
         if out is None:
             out = torch.empty((M, I), dtype=x.dtype, device=x.device)
+        if M == 0:
+            return out
         rc = _lib.lib().sfb200_sparse_gemm_swiglu(x.data_ptr(), x.stride(0), cw_gu.values.data_ptr(),
                                                   cw_gu.meta.data_ptr(), out.data_ptr(), out.stride(0),
                                                   M, I, cw_gu.K, _dt(x), _stream())
@@ -203,6 +207,8 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
         up = up.contiguous()
     with torch.cuda.device(gate.device):
         out = torch.empty(gate.shape, dtype=gate.dtype, device=gate.device)
+        if gate.numel() == 0:
+            return out
         rc = _lib.lib().sfb200_silu_mul(gate.data_ptr(), gate.stride(0), up.data_ptr(), up.stride(0),
                                         out.data_ptr(), out.stride(0), gate.shape[0], gate.shape[1],
                                         _dt(gate), _stream())

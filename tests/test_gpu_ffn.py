@@ -246,3 +246,26 @@ def test_model_surgery_replaces_every_mlp():
         err = (got.float() - w.float()).abs().max().item()
         assert err <= 3e-2 * w.float().pow(2).mean().sqrt().item() + 2.0 ** -8 * w.float().abs().max().item()
     assert ops.device_status() == 0
+
+
+def test_empty_batch_returns_empty_outputs():
+    """Zero tokens: every entry of the Python surface returns an empty tensor of the right shape and
+    launches nothing (the C ABI itself rejects M <= 0 as an invalid argument)."""
+    dt, H, I = "bf16", 256, 512
+    (gp, up, dp), _ = _linears(H, I, dt, prune=True)
+    x0 = torch.zeros(0, H, device="cuda", dtype=torch.bfloat16)
+    cw = ops.compress_weight(gp.weight.data)
+    assert ops.sparse_gemm(x0, cw).shape == (0, I)
+    assert ops.sparse_gemm_swiglu(x0, ops.compress_gate_up(gp.weight.data, up.weight.data)).shape == (0, I)
+    assert ops.silu_mul(torch.zeros(0, I, device="cuda", dtype=torch.bfloat16),
+                        torch.zeros(0, I, device="cuda", dtype=torch.bfloat16)).shape == (0, I)
+    for mode in ("sparse", "dense", "auto"):
+        assert SparseFlowFusedMLP(gp, up, dp, force_mode=mode)(x0).shape == (0, H)
+        assert SparseFlowFusedMLP(gp, up, dp, force_mode=mode)(x0.view(0, 7, H)[:0]).shape[-1] == H
+    lin = SparseFlowLinear(gp.weight.data, None, policy=SparseFlowPolicy(min_M_default=1), dense_uses_pruned=True)
+    assert lin(x0).shape == (0, I)
+    from sparseflow_b200 import _lib
+    rc = _lib.lib().sfb200_sparse_gemm(x0.data_ptr(), H, cw.values.data_ptr(), cw.meta.data_ptr(), x0.data_ptr(), I,
+                                       0, I, H, 1, None, 0, None)
+    assert rc == 1
+    assert ops.device_status() == 0
