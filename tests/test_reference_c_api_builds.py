@@ -3,7 +3,7 @@
 ``tests/test_c_api.cpp`` of the reference includes ``"../runtime/api/sparseflow_api.h"``; a shim header
 at that relative path forwards to ``include/sparseflow_b200.h``.  The source is compiled where it
 lies in a checkout of the reference (never copied); the test is skipped when no checkout is
-present (``SPARSEFLOW_REFERENCE`` or ``/root/reference``).  No GPU needed: with the inputs of that
+present (``SPARSEFLOW_REFERENCE``, default: a ``reference`` folder beside this repository).  No GPU needed: with the inputs of that
 test the dispatcher never launches a kernel."""
 import os
 import shutil
@@ -14,7 +14,7 @@ import pytest
 from sparseflow_b200 import _lib
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = os.environ.get("SPARSEFLOW_REFERENCE", "/root/reference")
+REF = os.environ.get("SPARSEFLOW_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference"))
 SRC = os.path.join(REF, "tests", "test_c_api.cpp")
 
 
