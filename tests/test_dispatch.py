@@ -70,3 +70,53 @@ def test_policy_low_band_and_defaults_follow_the_measured_table():
     assert not pol.should_use_sparse("down_proj", 65) and not pol.should_use_sparse("down_proj", 511)
     assert pol.should_use_sparse("down_proj", 512)
     assert not pol.should_use_sparse("k_proj", 1) and pol.should_use_sparse("k_proj", 2048)
+
+
+def test_op_level_gate_with_overrides(tmp_path):
+    """Truth table of decide(): overrides first, then low band, then [lo, hi]; reasons agree with decisions."""
+    from sparseflow_b200 import shape_gate as sg
+    ranges = {"ffn_gate": sg.GateRange(lo=256, hi=65536), "ffn_down": sg.GateRange(lo=512, hi=131072, decode_hi=64)}
+    ok, why = sg.decide("ffn_gate", 4, 64, ranges=ranges)
+    assert ok and why == "gate:run (lo=256 <= M_eff=256 <= hi=65536)"
+    ok, why = sg.decide("ffn_gate", 1, 255, ranges=ranges)
+    assert not ok and why == "gate:skip (M_eff=255 < lo=256)"
+    ok, why = sg.decide("ffn_gate", 1024, 65, ranges=ranges)
+    assert not ok and "> hi=65536" in why
+    assert sg.decide("ffn_down", 8, 8, ranges=ranges) == (True, "gate:run (M_eff=64 <= decode_hi=64)")
+    assert sg.decide("ffn_down", 5, 13, ranges=ranges)[0] is False
+    assert sg.decide("lm_head", 1, 4096, ranges=ranges) == (False, "no-range:default-dense")
+    assert sg.decide("ffn_down", 0, 7, ranges=ranges)[0] is False
+    assert sg.decide_sparse_sm89 is sg.decide_sparse_sm100
+    # default ranges come from the measured table
+    r = sg.default_ranges()
+    assert r["ffn_gate"].lo == dispatch.THRESHOLDS["ffn_gate_up"] and r["attn_qkv"].decode_hi == dispatch.DECODE_MAX_M["attn_proj"]
+    # overrides generated with the reference's rule
+    results = [
+        {"shape": "ffn_gate", "batch": 1, "seq_len": 128, "speedup": 1.5, "skipped": False, "acc_gate_pass": True},
+        {"shape": "ffn_gate", "batch": 1, "seq_len": 128, "speedup": 1.1, "skipped": False},          # worse duplicate
+        {"shape": "ffn_gate", "batch": 64, "seq_len": 64, "speedup": 1.9, "acc_gate_pass": False},
+        {"shape": "ffn_down", "batch": 2, "seq_len": 512, "speedup": 1.05},
+        {"shape": "ffn_down", "batch": 2, "seq_len": 16, "speedup": 3.0, "skipped": True, "shape_gate": "M too small"},
+        {"shape": "attn_qkv", "batch": 1, "seq_len": 1, "speedup": None},
+        {"batch": 1}, "junk",
+    ]
+    doc = sg.make_overrides(results, min_speedup=1.2, source_run="run.json", run_id="r1")
+    ov = doc["overrides"]
+    assert ov["ffn_gate|b=1|s=128"]["decision"] == "sparse" and ov["ffn_gate|b=1|s=128"]["speedup"] == 1.5
+    assert ov["ffn_gate|b=64|s=64"] == {"decision": "dense", "reason": "acc_gate_fail", "speedup": 1.9, "acc_max_err_pct": None}
+    assert ov["ffn_down|b=2|s=512"]["reason"] == "speedup=1.050<min"
+    assert ov["ffn_down|b=2|s=16"]["reason"] == "skipped (M too small)"
+    assert ov["attn_qkv|b=1|s=1"]["reason"] == "no-speedup" and len(ov) == 5
+    p = tmp_path / "ov.json"
+    p.write_text(json.dumps(doc))
+    o = sg.ShapeOverrides(str(p))
+    assert o.min_speedup == 1.2 and o.src == "run.json"
+    assert sg.decide("ffn_gate", 1, 128, overrides=o, ranges=ranges) == (True, "override:sparse (speedup=1.500>=min)")
+    assert sg.decide("ffn_gate", 64, 64, overrides=o, ranges=ranges) == (False, "override:dense (acc_gate_fail)")
+    assert sg.decide("ffn_gate", 4, 64, overrides=o, ranges=ranges)[1].startswith("gate:run")     # no override: range gate
+    assert sg.ShapeOverrides(str(tmp_path / "missing.json")).map == {}
+    import pytest
+    with pytest.raises(FileNotFoundError):
+        sg.ShapeOverrides(str(tmp_path / "missing.json"), strict=True)
+    with pytest.raises(ValueError):
+        sg.make_overrides([{"batch": 1}])
