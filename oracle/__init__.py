@@ -19,6 +19,7 @@ from .sparse24 import (  # noqa: F401
     hw_meta_tiled,
     hw_meta_tiled_to_nibbles,
     ref_codes_to_pairs,
+    ref_codes_packed_bytes,
     enum_codes_kmajor,
     nibble_words_rowmajor,
     decompress,

@@ -191,6 +191,14 @@ def enum_codes_kmajor(idx0, idx1) -> np.ndarray:
     return np.ascontiguousarray(lut[idx0, idx1].T).reshape(-1)
 
 
+def ref_codes_packed_bytes(ref_codes: np.ndarray) -> np.ndarray:
+    """PAIR_TO_CODE nibbles two groups per byte, even group in the low nibble: [R, K/8] uint8
+    (experiments/gen_test_artifacts.py:20-53; 16 bytes per row at K = 128)."""
+    c = ref_codes.astype(np.uint8)
+    assert c.shape[1] % 2 == 0
+    return ((c[:, 0::2] & 0xF) | ((c[:, 1::2] & 0xF) << 4)).astype(np.uint8)
+
+
 def ref_codes_to_pairs(codes: np.ndarray):
     """Invert PAIR_TO_CODE (experiments/prune_24_cpu.py:12-15)."""
     inv0 = np.full(256, 255, np.uint8)

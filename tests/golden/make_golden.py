@@ -42,6 +42,16 @@ def main(ref_root: str) -> None:
             with open(os.path.join(HERE, f), "rb") as fh:
                 manifest["files"][f] = hashlib.sha256(fh.read()).hexdigest()
 
+    # Nibble-packed code bytes (two groups per byte) from the reference's artifact generator, run as is.
+    with tempfile.TemporaryDirectory() as tmp:
+        subprocess.run([sys.executable, os.path.join(exp, "gen_test_artifacts.py")], cwd=tmp, check=True,
+                       stdout=subprocess.DEVNULL)
+        with open(os.path.join(tmp, "dA.bin"), "rb") as fh:           # same seed-0 matrix: same compressed values
+            assert hashlib.sha256(fh.read()).hexdigest() == manifest["files"]["dA.bin"]
+        shutil.copy(os.path.join(tmp, "dE_case_0.bin"), os.path.join(HERE, "dE_case_0.bin"))
+        with open(os.path.join(HERE, "dE_case_0.bin"), "rb") as fh:
+            manifest["files"]["dE_case_0.bin"] = hashlib.sha256(fh.read()).hexdigest()
+
     # Tie / special-value patterns: the reference's selection expression run as is.
     pats = []
     for ranks in itertools.product(range(3), repeat=4):

@@ -114,3 +114,41 @@ def test_ffn_oracle_composition():
     np.testing.assert_allclose(r["out_f32"], out.numpy(), rtol=2e-2, atol=2e-2)
     src = o.interleave_gate_up_rows(I, 16)
     assert src[:16].tolist() == list(range(16)) and src[16:32].tolist() == list(range(I, I + 16))
+
+
+def test_packed_code_bytes_match_reference_artifact():
+    """The reference's gen_test_artifacts.py (run unmodified by make_golden.py) packs the code nibbles two
+    groups per byte; same seed-0 matrix as the main fixture."""
+    import os
+    g = os.path.join(os.path.dirname(__file__), "golden")
+    codes = np.fromfile(os.path.join(g, "dE.bin"), dtype=np.uint8).reshape(128, 32)
+    want = np.fromfile(os.path.join(g, "dE_case_0.bin"), dtype=np.uint8).reshape(128, 16)
+    assert np.array_equal(o.ref_codes_packed_bytes(codes), want)
+
+
+def test_product_side_encoding_converters_agree_with_the_oracle():
+    """sparseflow_b200.encodings (torch index arithmetic, any device) against the numpy oracle."""
+    import os
+    import torch
+    from sparseflow_b200 import encodings as enc
+    rng = np.random.default_rng(3)
+    w = rng.standard_normal((200, 320)).astype(np.float16).view(np.uint16)
+    r = o.prune_24(w, "f16")
+    codes = torch.from_numpy(r["ref_codes"])
+    nib = enc.codes_to_nibbles(codes)
+    assert np.array_equal(nib.numpy(), o.hw_nibbles(r["idx0"], r["idx1"]))
+    assert torch.equal(enc.nibbles_to_codes(nib), codes)
+    assert np.array_equal(enc.enum_kmajor(nib).numpy().view(np.uint16), o.enum_codes_kmajor(r["idx0"], r["idx1"]))
+    assert np.array_equal(enc.nibble_words(nib).numpy().view(np.uint32), o.nibble_words_rowmajor(r["idx0"], r["idx1"]))
+    assert np.array_equal(enc.packed_code_bytes(codes).numpy(), o.ref_codes_packed_bytes(r["ref_codes"]))
+    tiled = torch.from_numpy(o.hw_meta_tiled(r["idx0"], r["idx1"]).view(np.uint8).reshape(-1).copy())
+    assert torch.equal(enc.tiled_meta_to_nibbles(tiled, 200, 320), nib)
+    g = os.path.join(os.path.dirname(__file__), "golden")
+    gold = torch.from_numpy(np.fromfile(os.path.join(g, "dE.bin"), dtype=np.uint8).reshape(128, 32))
+    want = np.fromfile(os.path.join(g, "dE_case_0.bin"), dtype=np.uint8).reshape(128, 16)
+    assert np.array_equal(enc.packed_code_bytes(gold).numpy(), want)
+    import pytest
+    with pytest.raises(ValueError):
+        enc.codes_to_nibbles(torch.tensor([[7]], dtype=torch.uint8))
+    with pytest.raises(ValueError):
+        enc.nibbles_to_codes(torch.tensor([[5]], dtype=torch.uint8))      # idx0 == idx1
