@@ -116,3 +116,22 @@ def test_prune_24_dense_weight_api():
         prune_24_dense_weight(torch.zeros(4, 8, dtype=torch.float32, device="cuda"))
     with pytest.raises(ValueError):
         prune_24_dense_weight(torch.zeros(8, dtype=torch.float16, device="cuda"))
+
+
+def test_full_size_tiled_metadata_equals_code_bytes_llama_gate():
+    """Size-independent consistency at the benchmark's weight size (11008 x 4096): the sm_100 tile layout,
+    un-tiled on the device, names the same index pairs as the per-group code bytes of the same launch, and
+    the three harness encodings round-trip through them."""
+    from sparseflow_b200 import encodings as enc
+    g = torch.Generator(device="cuda").manual_seed(11)
+    w = (torch.randn(11008, 4096, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    out = ops.prune_compress_24(w, want_ref_codes=True)
+    nib = enc.tiled_meta_to_nibbles(out["meta"], 11008, 4096)
+    assert torch.equal(nib, enc.codes_to_nibbles(out["ref_codes"]))
+    assert torch.equal(enc.nibbles_to_codes(nib), out["ref_codes"])
+    words = enc.nibble_words(nib)
+    assert words.shape == (11008, 128)
+    back = (words.to(torch.int64).unsqueeze(-1) >> (4 * torch.arange(8, device="cuda"))) & 0xF
+    assert torch.equal(back.reshape(11008, 1024).to(torch.uint8), nib)
+    assert enc.enum_kmajor(nib).shape == (11008 * 1024,) and int(enc.enum_kmajor(nib).max()) == 5
+    assert enc.packed_code_bytes(out["ref_codes"]).shape == (11008, 512)
