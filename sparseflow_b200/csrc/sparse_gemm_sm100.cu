@@ -353,6 +353,37 @@ int launch_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
 }
 
+// Kernel / token-tile choice for 128 < tokens < kPairMinTokens.  In this range every candidate is bound
+// by operand traffic, not by the tensor pipe, and what decides is how many passes ("waves") the tile count
+// needs on the available SMs.  Cost of a candidate = waves x K steps x time per 64-wide K step + a fixed
+// launch/prologue/epilogue term, with the step time taken from measurements on B200:
+//   single-CTA tile of bn tokens: a step moves 9 KiB (values + metadata) + bn x 128 B (tokens); an SM
+//     sustains about 145 GB/s of operand traffic, all SMs together about 19.5 TB/s out of L2 (17 TB/s
+//     for the 256-token tile, whose ring is only four stages deep);
+//   CTA-pair tile (256 rows x 256 tokens): 275 ns per step, 6 us fixed; taken only when it wins by 3 %.
+// Returns 128 / 192 / 256 (single-CTA token tile) or 1256 (CTA-pair kernel).
+int pick_mid_variant(int n_out, int m_tok, int K, int num_sms) {
+  const double k64 = (K + 63) / 64;
+  const long mb = (n_out + 127) / 128;
+  double best = 1e30;
+  int pick = 128;
+  const int cands[3] = {128, 192, 256};
+  for (int bn : cands) {
+    const long tiles = mb * ((m_tok + bn - 1) / bn);
+    const long waves = (tiles + num_sms - 1) / num_sms;
+    const double active = tiles < num_sms ? static_cast<double>(tiles) : static_cast<double>(num_sms);
+    const double bytes = 9216.0 + bn * 128.0;
+    const double per_sm = bytes / 145e9, shared = active * bytes / (bn == 256 ? 17e12 : 19.5e12);
+    const double cost = waves * k64 * (per_sm > shared ? per_sm : shared) + 4e-6;
+    if (cost < best) { best = cost; pick = bn; }
+  }
+  const int pairs = num_sms / 2 > 0 ? num_sms / 2 : 1;
+  const long ptiles = static_cast<long>((n_out + 255) / 256) * ((m_tok + 255) / 256);
+  const double pcost = static_cast<double>((ptiles + pairs - 1) / pairs) * k64 * 275e-9 + 6e-6;
+  if (pcost < 0.97 * best) pick = 1256;
+  return pick;
+}
+
 template <int EPI>
 int dispatch_bn(const SparseGemmArgs& a, cudaStream_t stream) {
   int bn = a.force_bn;
@@ -360,8 +391,12 @@ int dispatch_bn(const SparseGemmArgs& a, cudaStream_t stream) {
     if (a.m_tok <= 32) bn = 32;
     else if (a.m_tok <= 64) bn = 64;
     else if (a.m_tok <= 128) bn = 128;
-    else if (a.m_tok <= 1024) bn = 128;
-    else bn = 256;
+    else bn = pick_mid_variant(a.n_out, a.m_tok, a.K, a.num_sms);
+  }
+  if (bn == 1256) {
+    SparseGemmArgs b = a;
+    b.force_bn = 1256;      // the variant the cost model was fitted on
+    return launch_sparse_gemm_pair(b, stream);
   }
   switch (bn) {
     case 32: return launch_cfg<Cfg<32, 64, 8, EPI>>(a, stream);
