@@ -221,6 +221,10 @@ SFB200_API int sfb200_blob_read_header(const void* header_host, size_t available
  * K slices and a 32/64/128-token tile.  No counterpart upstream. */
 SFB200_API int sfb200_debug_force_token_tile(int bn);
 
+/* The variant the library picks on its own for Y[M, N] = X[M, K] . W^T (swiglu = 1: the fused gate|up GEMM,
+ * N = 2 * I rows) on a GPU with num_sms SMs, in the numbering above; 0 for a non-positive size.  Host-only. */
+SFB200_API int sfb200_debug_plan_gemm(int M, int N, int K, int swiglu, int num_sms);
+
 /* Tuning hooks of sfb200_ffn_forward_host's copy/compute pipeline: tokens are processed in chunks
  * of `main_rows` while more than that remains, then the remainder is halved down to `tail_rows`
  * (small last chunks shorten what runs after the last host-to-device copy but run the GEMMs less

@@ -76,6 +76,7 @@ def lib() -> C.CDLL:
     L.sfb200_reduce_allgather.argtypes = [vp, i, i, i, C.POINTER(vp), i, vp, vp]
     L.sfb200_ffn_forward_noalloc.argtypes = [C.POINTER(FFNWeights), vp, i, vp, i, i, vp]
     L.sfb200_debug_force_token_tile.argtypes = [i]
+    L.sfb200_debug_plan_gemm.argtypes = [i, i, i, i, i]
     L.sfb200_debug_host_pipeline.argtypes = [i, i]
     L.sfb200_debug_host_chunk_plan.argtypes = [i, i, i, C.POINTER(C.c_int)]
     L.sfb200_blob_bytes.restype = sz

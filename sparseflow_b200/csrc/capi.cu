@@ -361,6 +361,13 @@ SFB200_API int sfb200_debug_force_token_tile(int bn) {
   return kOk;
 }
 
+/* Which kernel variant sfb200_sparse_gemm (swiglu = 0) or sfb200_sparse_gemm_swiglu (swiglu = 1, N = 2 * I
+ * rows) runs for a shape on a GPU with num_sms SMs, in the numbering of sfb200_debug_force_token_tile.  Host-only. */
+SFB200_API int sfb200_debug_plan_gemm(int M, int N, int K, int swiglu, int num_sms) {
+  if (M <= 0 || N <= 0 || K <= 0 || num_sms <= 0) return 0;
+  return plan_sparse_gemm(M, N, K, swiglu ? kEpiSwiGLU : kEpiStore, num_sms);
+}
+
 /* The chunk plan sfb200_ffn_forward_host would use for M tokens (host-only; out8 holds 8 ints). */
 SFB200_API int sfb200_debug_host_chunk_plan(int M, int main_rows, int tail_rows, int* out8) {
   if (M <= 0 || !out8) return 0;

@@ -70,6 +70,12 @@ int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream);
 // m_tok >= kPairMinTokens.  force_bn 1256 (256-row tiles) or 2192..2240 (512-row tiles) picks a variant.
 int launch_sparse_gemm_pair(const SparseGemmArgs& a, cudaStream_t stream);
 constexpr int kPairMinTokens = 1024;
+// Variant the CTA-pair launcher picks on its own (1256 or 2192..2240).
+int pick_pair_variant(int n_out, int m_tok, int K, int num_sms);
+// The kernel variant launch_sparse_gemm runs for a shape when nothing is forced, in the numbering of
+// SparseGemmArgs::force_bn: 8 decode kernel; 32..256 single-CTA kernel with that token tile; 1256 / 2192..2240
+// CTA-pair kernel; 3000 + tile / 4000 + tile split-K cluster kernel with 2 / 4 K slices.  Host-only.
+int plan_sparse_gemm(int m_tok, int n_out, int K, int epi, int num_sms);
 // Row-parallel GEMM of a tensor-parallel FFN with the reduce-scatter fused into the epilogue:
 // token block o of this rank's partial output is stored into peer_slots[o] (rank o's receive slot
 // for this rank, [tok_per_owner, n_out], peer-mapped memory).

@@ -367,7 +367,7 @@ int pick_mid_variant(int n_out, int m_tok, int K, int num_sms) {
   const long mb = (n_out + 127) / 128;
   double best = 1e30;
   int pick = 128;
-  const int cands[3] = {128, 192, 256};
+  const int cands[3] = {128, 192, 256};   // a 64-token tile costs the same per step (latency-bound ring): measured no gain
   for (int bn : cands) {
     const long tiles = mb * ((m_tok + bn - 1) / bn);
     const long waves = (tiles + num_sms - 1) / num_sms;
@@ -386,18 +386,7 @@ int pick_mid_variant(int n_out, int m_tok, int K, int num_sms) {
 
 template <int EPI>
 int dispatch_bn(const SparseGemmArgs& a, cudaStream_t stream) {
-  int bn = a.force_bn;
-  if (bn == 0) {
-    if (a.m_tok <= 32) bn = 32;
-    else if (a.m_tok <= 64) bn = 64;
-    else if (a.m_tok <= 128) bn = 128;
-    else bn = pick_mid_variant(a.n_out, a.m_tok, a.K, a.num_sms);
-  }
-  if (bn == 1256) {
-    SparseGemmArgs b = a;
-    b.force_bn = 1256;      // the variant the cost model was fitted on
-    return launch_sparse_gemm_pair(b, stream);
-  }
+  const int bn = a.force_bn;
   switch (bn) {
     case 32: return launch_cfg<Cfg<32, 64, 8, EPI>>(a, stream);
     case 64: return launch_cfg<Cfg<64, 64, 8, EPI>>(a, stream);
@@ -410,31 +399,35 @@ int dispatch_bn(const SparseGemmArgs& a, cudaStream_t stream) {
 
 }  // namespace
 
+int plan_sparse_gemm(int m_tok, int n_out, int K, int epi, int num_sms) {
+  // few row tiles (the weight has fewer 128-row tiles than half the SMs) and fewer tokens than the
+  // prefill kernel wants: split K over a cluster so that the weight is streamed by (nearly) every SM
+  const int split = (epi == kEpiStore && m_tok < kPairMinTokens) ? splitk_factor(m_tok, n_out, K, num_sms) : 1;
+  // decode-sized token counts: bandwidth kernel on warp-level mma.sp; measured against the split-K
+  // kernel it only wins at 1-2 tokens when both apply
+  if (m_tok <= kSmallMMaxTokens && (split == 1 || m_tok <= 2)) return 8;
+  if (m_tok >= kPairMinTokens) return pick_pair_variant(n_out, m_tok, K, num_sms);
+  if (split > 1) return (split == 4 ? 4000 : 3000) + splitk_token_tile(m_tok);
+  if (m_tok <= 32) return 32;
+  if (m_tok <= 64) return 64;
+  if (m_tok <= 128) return 128;
+  return pick_mid_variant(n_out, m_tok, K, num_sms);
+}
+
 int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream) {
   if (a.K % 64 != 0 || a.K <= 0 || a.m_tok <= 0 || a.n_out <= 0) return kErrInvalid;
   if (a.n_out % 8 != 0 || a.ldx % 8 != 0 || a.ldy % 8 != 0) return kErrInvalid;
   if ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.values) |
        reinterpret_cast<uintptr_t>(a.meta) | reinterpret_cast<uintptr_t>(a.y)) & 15)
     return kErrInvalid;
-  // few row tiles (the weight has fewer 128-row tiles than half the SMs) and fewer tokens than the
-  // prefill kernel wants: split K over a cluster so that the weight is streamed by (nearly) every SM
-  const int split = (a.force_bn == 0 && a.epi == kEpiStore && a.m_tok < kPairMinTokens)
-                        ? splitk_factor(a.m_tok, a.n_out, a.K, a.num_sms) : 1;
-  // decode-sized token counts: bandwidth kernel on warp-level mma.sp (force with 8, avoid with any other
-  // tile); measured against the split-K kernel it only wins at 1-2 tokens when both apply
-  if (a.force_bn == 8 || (a.force_bn == 0 && a.m_tok <= kSmallMMaxTokens && (split == 1 || a.m_tok <= 2)))
-    return launch_sparse_gemm_small_m(a, stream);
-  // CTA-pair kernel for prefill-sized token counts (or when forced: 1256, 2192..2240)
-  if ((a.force_bn >= 1000 && a.force_bn < 3000) || (a.force_bn == 0 && a.m_tok >= kPairMinTokens))
-    return launch_sparse_gemm_pair(a, stream);
-  // forced split-K: 3000 + token tile for 2 slices, 4000 + token tile for 4
-  if (a.force_bn >= 3000) return launch_sparse_gemm_splitk(a, a.force_bn >= 4000 ? 4 : 2, stream);
-  if (split > 1) return launch_sparse_gemm_splitk(a, split, stream);
-  if (a.epi == kEpiSwiGLU) {
-    if (a.n_out % 32 != 0 || (a.n_out / 2) % 8 != 0) return kErrInvalid;
-    return dispatch_bn<kEpiSwiGLU>(a, stream);
-  }
-  return dispatch_bn<kEpiStore>(a, stream);
+  if (a.epi == kEpiSwiGLU && (a.n_out % 32 != 0 || (a.n_out / 2) % 8 != 0)) return kErrInvalid;
+  SparseGemmArgs b = a;
+  if (b.force_bn == 0) b.force_bn = plan_sparse_gemm(a.m_tok, a.n_out, a.K, a.epi, a.num_sms);
+  const int v = b.force_bn;
+  if (v == 8) return launch_sparse_gemm_small_m(b, stream);
+  if (v >= 3000) return launch_sparse_gemm_splitk(b, v >= 4000 ? 4 : 2, stream);
+  if (v >= 1000) return launch_sparse_gemm_pair(b, stream);
+  return a.epi == kEpiSwiGLU ? dispatch_bn<kEpiSwiGLU>(b, stream) : dispatch_bn<kEpiStore>(b, stream);
 }
 
 }  // namespace sfb200

@@ -657,7 +657,7 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
 // through registers (about 30 units exposed); the 512-row kernel streams two accumulators out in
 // chunks (about 90 units) but does twice the work per tile and can hit a whole number of waves
 // where 256-row tiles do not (e.g. a 4096-row weight at 4096 tokens: 144 tiles on 74 SM pairs).
-inline int pick_pair_variant(int n_out, int m_tok, int K, int pairs) {
+int pick_pair_variant_impl(int n_out, int m_tok, int K, int pairs) {
   const double kscale = 4096.0 / (K > 0 ? K : 4096);
   auto waves = [&](long tiles) { return static_cast<double>((tiles + pairs - 1) / pairs); };
   const long t1 = static_cast<long>((n_out + 255) / 256) * ((m_tok + 255) / 256);
@@ -679,7 +679,7 @@ int dispatch_pair(const SparseGemmArgs& a, cudaStream_t stream) {
   // force_bn: 1256 = 256-row tiles with 256 tokens; 2192 / 2208 / 2224 / 2240 =
   // 512-row tiles with that many tokens.  0 = automatic.
   int v = a.force_bn;
-  if (v == 0) v = pick_pair_variant(a.n_out, a.m_tok, a.K, a.num_sms / 2);
+  if (v == 0) v = pick_pair_variant_impl(a.n_out, a.m_tok, a.K, a.num_sms / 2);
   switch (v) {
     case 1256: return launch_pair_cfg<PairCfg<256, 128, 4, 1, EPI>>(a, stream);
     case 1257: return launch_pair_cfg<PairCfg<256, 64, 8, 1, EPI>>(a, stream);   // same tile, 64-wide stages
@@ -692,6 +692,10 @@ int dispatch_pair(const SparseGemmArgs& a, cudaStream_t stream) {
 }
 
 }  // namespace
+
+int pick_pair_variant(int n_out, int m_tok, int K, int num_sms) {
+  return pick_pair_variant_impl(n_out, m_tok, K, num_sms / 2 > 0 ? num_sms / 2 : 1);
+}
 
 int launch_sparse_gemm_pair_scatter(const SparseGemmArgs& a, void* const* peer_slots, int tp, int tok_per_owner,
                                     cudaStream_t stream) {

@@ -177,3 +177,27 @@ def test_host_pipeline_chunk_plan_covers_every_token():
     n = L.sfb200_debug_host_chunk_plan(4096, 0, 0, out)
     assert list(out[:n]) == [1024] * 4
     assert L.sfb200_debug_host_chunk_plan(0, 0, 0, out) == 0 and L.sfb200_debug_host_chunk_plan(8, 0, 0, None) == 0
+
+
+def test_kernel_plan_per_shape():
+    """Which kernel the dispatcher runs for the benchmark shapes on a 148-SM GPU (host-only planning call)."""
+    from sparseflow_b200 import _lib
+    plan = lambda M, N, K, sw=0: _lib.lib().sfb200_debug_plan_gemm(M, N, K, sw, 148)
+    # decode: many row tiles -> warp-level kernel up to 8 tokens; few row tiles -> it keeps only 1-2 tokens
+    assert plan(1, 28672, 4096) == 8 and plan(8, 28672, 4096) == 8 and plan(8, 22016, 4096, 1) == 8
+    assert plan(2, 4096, 14336) == 8 and plan(4, 4096, 14336) == 4032
+    # few row tiles, below the prefill threshold: split-K over a cluster, 4 slices for 32 tiles, 2 for 64
+    assert plan(32, 4096, 11008) == 4032 and plan(64, 4096, 11008) == 4064 and plan(128, 4096, 4096) == 4128
+    assert plan(16, 8192, 8192) == 3032 and plan(64, 8192, 8192) == 3064
+    assert plan(128, 8192, 8192) == 128               # two slices of a 128-token tile do not pay
+    assert plan(32, 512, 256) == 32                   # too little K to split (< 4 metadata tiles per slice)
+    # many row tiles, up to 128 tokens: single-CTA kernel with the smallest covering token tile
+    assert plan(9, 22016, 4096) == 32 and plan(33, 22016, 4096) == 64 and plan(100, 22016, 4096) == 128
+    assert plan(64, 22016, 4096, 1) == 64             # the SwiGLU epilogue has no split-K form
+    # 129..1023 tokens: cost model over tile waves
+    assert plan(512, 14336, 4096) == 1256 and plan(512, 22016, 4096, 1) == 1256
+    assert plan(256, 14336, 4096) == 256 and plan(512, 11008, 4096) == 192 and plan(512, 4096, 14336) == 128
+    # prefill: CTA-pair kernel, 512-row tiles where they fill the waves better
+    assert plan(4096, 22016, 4096, 1) == 1256 and plan(4096, 4096, 11008) == 2240
+    assert plan(1024, 4096, 4096) in (1256, 2192, 2208, 2224, 2240)
+    assert plan(0, 4096, 4096) == 0
