@@ -67,7 +67,8 @@ struct Cfg {
   static constexpr int OFF_E = OFF_B + STAGES * B_BYTES;
   static constexpr int OFF_D = OFF_E + STAGES * E_BYTES;
   static constexpr int OFF_BAR = OFF_D + 2 * D_BYTES;
-  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;  // + barriers + alignment slack
+  static constexpr int BAR_BYTES = ((8 * (2 * STAGES + 4) + 16) + 127) & ~127;   // barriers + tmem slot + error flag
+  static constexpr int SMEM_BYTES = OFF_BAR + BAR_BYTES + 1024;  // + alignment slack
   static_assert(BK == 64 || BK == 128, "BK");
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "BN");
   static_assert(TMEM_USED <= 512, "tmem");
@@ -388,8 +389,8 @@ template <int EPI>
 int dispatch_bn(const SparseGemmArgs& a, cudaStream_t stream) {
   const int bn = a.force_bn;
   switch (bn) {
-    case 32: return launch_cfg<Cfg<32, 64, 8, EPI>>(a, stream);
-    case 64: return launch_cfg<Cfg<64, 64, 8, EPI>>(a, stream);
+    case 32: return launch_cfg<Cfg<32, 64, 14, EPI>>(a, stream);   // deep rings: a K step completes per latency / stages
+    case 64: return launch_cfg<Cfg<64, 64, 11, EPI>>(a, stream);
     case 128: return launch_cfg<Cfg<128, 64, 8, EPI>>(a, stream);
     case 192: return launch_cfg<Cfg<192, 64, 6, EPI>>(a, stream);
     case 256: return launch_cfg<Cfg<256, 64, 4, EPI>>(a, stream);
