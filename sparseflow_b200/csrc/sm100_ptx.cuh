@@ -98,15 +98,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // first failure for the host to read.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* err,
                                           int* gstatus, int where) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
-  while (true) {
+  // Polls only, first: reading %globaltimer costs on the order of a pipeline stage (measured: a
+  // wait that consulted it on every miss put ~190 ns under every K step of every kernel), so the
+  // clock and the error flag are looked at once per 64 missed polls.
+  unsigned long long t0 = 0;
+  for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (*err) return false;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) {
-      *err = 1;
-      atomicCAS(gstatus, 0, (kStatusWaitTimeout << 8) | where);
-      return false;
+    if ((it & 63u) == 0) {
+      if (*err) return false;
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) {
+        *err = 1;
+        atomicCAS(gstatus, 0, (kStatusWaitTimeout << 8) | where);
+        return false;
+      }
     }
   }
 }
