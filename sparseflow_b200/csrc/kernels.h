@@ -94,9 +94,9 @@ int splitk_factor(int m_tok, int n_out, int K, int num_sms);
 int splitk_token_tile(int m_tok);
 
 // ---- small-M (decode) sparse GEMM ----------------------------------------------------------
-// M <= 32 tokens; chosen by launch_sparse_gemm for m_tok <= kSmallMMaxTokens (force_bn == 8 forces it).
+// Supports M <= 32 tokens; chosen by launch_sparse_gemm for m_tok <= kSmallMMaxTokens (force_bn == 8 forces it).
 int launch_sparse_gemm_small_m(const SparseGemmArgs& a, cudaStream_t stream);
-constexpr int kSmallMMaxTokens = 8;
+constexpr int kSmallMMaxTokens = 4;   // from 5 tokens the tcgen05 kernel with a 32-token tile is faster (measured)
 
 // ---- elementwise -----------------------------------------------------------------------------
 // out[m, i] = silu(gu[m, i]) * gu[m, I + i]   (unfused variant, gate|up concatenated along columns)

@@ -389,9 +389,10 @@ template <int EPI>
 int dispatch_bn(const SparseGemmArgs& a, cudaStream_t stream) {
   const int bn = a.force_bn;
   switch (bn) {
-    case 32: return launch_cfg<Cfg<32, 64, 14, EPI>>(a, stream);   // deep rings: a K step completes per latency / stages
-    case 64: return launch_cfg<Cfg<64, 64, 11, EPI>>(a, stream);
-    case 128: return launch_cfg<Cfg<128, 64, 8, EPI>>(a, stream);
+    // 128-wide stages: the per-stage handshake (~160-190 ns), not the bytes, paces the K loop of the small tiles
+    case 32: return launch_cfg<Cfg<32, 128, 7, EPI>>(a, stream);
+    case 64: return launch_cfg<Cfg<64, 128, 6, EPI>>(a, stream);
+    case 128: return launch_cfg<Cfg<128, 128, 4, EPI>>(a, stream);
     case 192: return launch_cfg<Cfg<192, 64, 6, EPI>>(a, stream);
     case 256: return launch_cfg<Cfg<256, 64, 4, EPI>>(a, stream);
     default: return kErrInvalid;

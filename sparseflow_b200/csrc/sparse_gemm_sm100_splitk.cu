@@ -38,13 +38,17 @@ struct SplitKParams {
   int fmt, act;
 };
 
+// One pipeline stage = one 128-wide K tile = one metadata tile.  (With 64-wide stages the K loop ran at
+// one stage per ~160-190 ns whatever the tile held: the per-stage handshake, not the bytes, set the
+// pace, so stages are made as wide as the 128-byte swizzle of the A operand allows.)
 template <int BN_, int STAGES_>
 struct SkCfg {
-  static constexpr int BM = 128, BK = 64;
+  static constexpr int BM = 128, BK = 128;
   static constexpr int BN = BN_, STAGES = STAGES_;
-  static constexpr int A_BYTES = BM * (BK / 2) * 2;   // 8 KiB
-  static constexpr int B_BYTES = BN * 128;            // BN tokens x 64 elements
-  static constexpr int E_BYTES = 2048;                // one 128 x 128 metadata tile per two stages
+  static constexpr int A_BYTES = BM * (BK / 2) * 2;   // 16 KiB, 128-byte swizzle
+  static constexpr int B_SUB_BYTES = BN * 128;        // BN tokens x 64 elements
+  static constexpr int B_BYTES = 2 * B_SUB_BYTES;
+  static constexpr int E_BYTES = 2048;                // one 128 x 128 metadata tile per stage
   static constexpr int SLOT_BYTES = BN * BM * 4;      // S slots x BN tokens x 128/S features, fp32
   static constexpr int TMEM_USED = BN + 4 * STAGES;
   static constexpr int TMEM_COLS = TMEM_USED <= 64 ? 64 : TMEM_USED <= 128 ? 128 : TMEM_USED <= 256 ? 256 : 512;
@@ -55,7 +59,7 @@ struct SkCfg {
   static constexpr int OFF_BAR = OFF_SLOT + SLOT_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 128, "BN");
-  static_assert(STAGES % 2 == 0, "metadata tiles span two stages");
+  static_assert(8 * (2 * STAGES + 1) + 16 <= 256, "barrier area");
   static_assert(SMEM_BYTES <= 232448, "smem");
 };
 
@@ -95,9 +99,8 @@ sparse_gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
   const int base = p.k_tiles128 / S, extra = p.k_tiles128 % S;
   const int t_begin = rank * base + (rank < extra ? rank : extra);
   const int t_count = base + (rank < extra ? 1 : 0);
-  const int k_total = p.K / C::BK;
-  const int kt_begin = 2 * t_begin;
-  const int kt_end = (2 * (t_begin + t_count) < k_total) ? 2 * (t_begin + t_count) : k_total;
+  const int kt_begin = t_begin;              // stages are whole metadata tiles; a trailing half tile (K % 128 == 64)
+  const int kt_end = t_begin + t_count;      // is zero-filled by TMA
 
   if (threadIdx.x == 0) {
     *err = 0;
@@ -129,15 +132,13 @@ sparse_gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
       uint32_t ph = 0;
       for (int kt = kt_begin; kt < kt_end; ++kt) {
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, err, p.status, 1)) break;
-        const bool load_e = (kt & 1) == 0;
         const uint32_t full = bar_full + 8 * s;
-        mbar_arrive_expect_tx(full, C::A_BYTES + C::B_BYTES + (load_e ? C::E_BYTES : 0));
+        mbar_arrive_expect_tx(full, C::A_BYTES + C::B_BYTES + C::E_BYTES);
         tma_load_2d(sbase + C::OFF_A + s * C::A_BYTES, &tmA, kt * (C::BK / 2), m_blk * C::BM, full);
         tma_load_2d(sbase + C::OFF_B + s * C::B_BYTES, &tmB, kt * C::BK, n_blk * C::BN, full);
-        if (load_e) {
-          const uint32_t* src = p.meta + (static_cast<size_t>(m_blk) * p.k_tiles128 + (kt >> 1)) * 512;
-          bulk_load_1d(sbase + C::OFF_E + s * C::E_BYTES, src, C::E_BYTES, full);
-        }
+        tma_load_2d(sbase + C::OFF_B + s * C::B_BYTES + C::B_SUB_BYTES, &tmB, kt * C::BK + 64, n_blk * C::BN, full);
+        const uint32_t* src = p.meta + (static_cast<size_t>(m_blk) * p.k_tiles128 + kt) * 512;
+        bulk_load_1d(sbase + C::OFF_E + s * C::E_BYTES, src, C::E_BYTES, full);
         if (++s == C::STAGES) { s = 0; ph ^= 1; }
       }
     }
@@ -153,18 +154,15 @@ sparse_gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
         ok = mbar_wait(bar_full + 8 * s, ph, err, p.status, 2);
         if (!ok) break;
         tc_fence_after();
-        if ((kt & 1) == 0) {   // kt_begin is even: a slice always starts on a metadata tile
-          e_cols = C::BN + 4 * s;
-          tc_cp_128x128b(tmem_base + e_cols, make_smem_desc(sbase + C::OFF_E + s * C::E_BYTES, 0, 128, kSwNone));
-        }
+        e_cols = C::BN + 4 * s;
+        tc_cp_128x128b(tmem_base + e_cols, make_smem_desc(sbase + C::OFF_E + s * C::E_BYTES, 0, 128, kSwNone));
         const uint32_t a_addr = sbase + C::OFF_A + s * C::A_BYTES;
         const uint32_t b_addr = sbase + C::OFF_B + s * C::B_BYTES;
 #pragma unroll
-        for (int kb = 0; kb < 2; ++kb) {
-          const uint64_t adesc = make_smem_desc(a_addr + kb * 32, 16, 512, kSw64);
-          const uint64_t bdesc = make_smem_desc(b_addr + kb * 64, 16, 1024, kSw128);
-          const int ecol = (kt & 1) * 2 + kb;
-          tc_mma_sp_f16(tmem_base, adesc, bdesc, tmem_base + e_cols + (ecol & ~1), idesc | (ecol & 1),
+        for (int kb = 0; kb < 4; ++kb) {
+          const uint64_t adesc = make_smem_desc(a_addr + kb * 32, 16, 1024, kSw128);
+          const uint64_t bdesc = make_smem_desc(b_addr + (kb >> 1) * C::B_SUB_BYTES + (kb & 1) * 64, 16, 1024, kSw128);
+          tc_mma_sp_f16(tmem_base, adesc, bdesc, tmem_base + e_cols + (kb & ~1), idesc | (kb & 1),
                         (kt > kt_begin || kb > 0) ? 1u : 0u);
         }
         tc_commit(bar_empty + 8 * s);
@@ -268,7 +266,7 @@ int launch_sk(const SparseGemmArgs& a, int split, cudaStream_t stream) {
   }
   CUtensorMap tmA, tmB;
   const uint64_t kc = static_cast<uint64_t>(a.K) / 2;
-  if (!make_map_2d(&tmA, a.values, a.n_out, kc, kc * 2, C::BM, C::BK / 2, CU_TENSOR_MAP_SWIZZLE_64B, a.fmt))
+  if (!make_map_2d(&tmA, a.values, a.n_out, kc, kc * 2, C::BM, C::BK / 2, CU_TENSOR_MAP_SWIZZLE_128B, a.fmt))
     return kErrTensorMap;
   if (!make_map_2d(&tmB, a.x, a.m_tok, a.K, static_cast<uint64_t>(a.ldx) * 2, C::BN, 64,
                    CU_TENSOR_MAP_SWIZZLE_128B, a.fmt))
@@ -334,9 +332,9 @@ int launch_sparse_gemm_splitk(const SparseGemmArgs& a, int split, cudaStream_t s
     return kErrInvalid;
   int bn = a.force_bn >= 3000 ? a.force_bn % 1000 : splitk_token_tile(a.m_tok);
   switch (bn) {
-    case 32: return launch_sk<SkCfg<32, 12>>(a, split, stream);
-    case 64: return launch_sk<SkCfg<64, 10>>(a, split, stream);
-    case 128: return launch_sk<SkCfg<128, 6>>(a, split, stream);
+    case 32: return launch_sk<SkCfg<32, 7>>(a, split, stream);
+    case 64: return launch_sk<SkCfg<64, 5>>(a, split, stream);
+    case 128: return launch_sk<SkCfg<128, 3>>(a, split, stream);
     default: return kErrInvalid;
   }
 }

@@ -183,8 +183,9 @@ def test_kernel_plan_per_shape():
     """Which kernel the dispatcher runs for the benchmark shapes on a 148-SM GPU (host-only planning call)."""
     from sparseflow_b200 import _lib
     plan = lambda M, N, K, sw=0: _lib.lib().sfb200_debug_plan_gemm(M, N, K, sw, 148)
-    # decode: many row tiles -> warp-level kernel up to 8 tokens; few row tiles -> it keeps only 1-2 tokens
-    assert plan(1, 28672, 4096) == 8 and plan(8, 28672, 4096) == 8 and plan(8, 22016, 4096, 1) == 8
+    # decode: many row tiles -> warp-level kernel up to 4 tokens; few row tiles -> it keeps only 1-2 tokens
+    assert plan(1, 28672, 4096) == 8 and plan(4, 28672, 4096) == 8 and plan(4, 22016, 4096, 1) == 8
+    assert plan(5, 28672, 4096) == 32 and plan(8, 22016, 4096, 1) == 32
     assert plan(2, 4096, 14336) == 8 and plan(4, 4096, 14336) == 4032
     # few row tiles, below the prefill threshold: split-K over a cluster, 4 slices for 32 tiles, 2 for 64
     assert plan(32, 4096, 11008) == 4032 and plan(64, 4096, 11008) == 4064 and plan(128, 4096, 4096) == 4128
