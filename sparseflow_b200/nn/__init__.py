@@ -22,3 +22,4 @@ _safe_export("sparseflow_b200.nn.surgery", ["replace_llama_mlp_module"])
 _safe_export("sparseflow_b200.nn.sparseflow_linear", ["SparseFlowLinear", "make_sparseflow_linear", "prune_24_dense_weight"])
 _safe_export("sparseflow_b200.nn.sparseflow_mlp", ["SparseFlowMLP", "make_sparseflow_mlp"])
 _safe_export("sparseflow_b200.nn.sparse_linear", ["SparseLinear"])
+_safe_export("sparseflow_b200.nn.replace_llama", ["replace_llama_mlp", "replace_llama_full", "replace_llama_attention"])

@@ -20,8 +20,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .nn import (SparseFlowPolicy, make_sparseflow_linear, prune_24_dense_weight,
-                 replace_llama_mlp_module)
+from .nn import SparseFlowPolicy, prune_24_dense_weight, replace_llama_mlp_module
 
 
 class RMSNorm(nn.Module):
@@ -158,15 +157,9 @@ def time_arm(model, ids, iters, warmup):
 
 
 def sparsify_attention(model, policy) -> int:
-    n = 0
-    for layer in model.layers:
-        for name in ("q_proj", "k_proj", "v_proj", "o_proj"):
-            lin = getattr(layer.self_attn, name)
-            if isinstance(lin, nn.Linear):
-                setattr(layer.self_attn, name, make_sparseflow_linear(lin, policy=policy, op_name=name,
-                                                                      dense_uses_pruned=True))
-                n += 1
-    return n
+    """q/k/v/o of every layer through ``SparseFlowLinear`` (the MLPs were already swapped as whole modules)."""
+    from .nn.replace_llama import replace_llama_full
+    return replace_llama_full(model, policy, verbose=False, dense_uses_pruned=True)
 
 
 def run(layers=4, hidden=4096, inter=11008, heads=32, batch=2, seq=2048, dtype="bf16", iters=10, warmup=3,

@@ -269,3 +269,50 @@ def test_empty_batch_returns_empty_outputs():
                                        0, I, H, 1, None, 0, None)
     assert rc == 1
     assert ops.device_status() == 0
+
+
+def test_linear_level_surgery_mlp_and_attention():
+    """replace_llama_mlp / replace_llama_full (tools/llama_surgery.py, tools/llama_surgery_full.py): every projection of
+    every layer becomes a SparseFlowLinear carrying its op name; outputs match the dense layers on the pruned weights."""
+    from sparseflow_b200.nn.replace_llama import replace_llama_attention, replace_llama_full, replace_llama_mlp
+    H, I = 256, 512
+
+    def lin(i, o):
+        l = nn.Linear(i, o, bias=False, device="cuda", dtype=torch.bfloat16)
+        l.weight.data = ops.prune_compress_24(l.weight.data, want_values=False, want_meta=False, want_pruned=True)["pruned"]
+        return l
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.mlp = nn.Module()
+            self.mlp.gate_proj, self.mlp.up_proj, self.mlp.down_proj = lin(H, I), lin(H, I), lin(I, H)
+            self.self_attn = nn.Module()
+            for n in ("q_proj", "k_proj", "v_proj", "o_proj"):
+                setattr(self.self_attn, n, lin(H, H))
+
+    class Model(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.model = nn.Module()
+            self.model.layers = nn.ModuleList([Block(), Block()])
+
+    torch.manual_seed(1)
+    m = Model()
+    x = torch.randn(96, H, device="cuda", dtype=torch.bfloat16)
+    want = {(li, n): getattr(b.self_attn, n)(x) for li, b in enumerate(m.model.layers) for n in ("q_proj", "o_proj")}
+    want_g = m.model.layers[1].mlp.gate_proj(x)
+    pol = SparseFlowPolicy(min_M_gate_up=1, min_M_down=1, min_M_qkv=1, min_M_o=1)
+    assert replace_llama_mlp(m, pol, verbose=False) == 6
+    assert replace_llama_full(m, pol, verbose=False) == 8            # MLP already swapped: only the attention is left
+    assert replace_llama_attention(m, pol, verbose=False) == 0
+    b1 = m.model.layers[1]
+    assert isinstance(b1.mlp.gate_proj, SparseFlowLinear) and b1.mlp.gate_proj.op_name == "gate_proj"
+    assert b1.self_attn.k_proj.op_name == "k_proj"
+    for (li, n), ref in want.items():
+        got = getattr(m.model.layers[li].self_attn, n)(x)
+        assert (got.float() - ref.float()).abs().max() <= 1e-2 * ref.float().abs().max()
+    got_g = b1.mlp.gate_proj(x)
+    assert b1.mlp.gate_proj._sparse_count == 1
+    assert (got_g.float() - want_g.float()).abs().max() <= 1e-2 * want_g.float().abs().max()
+    assert ops.device_status() == 0
