@@ -209,3 +209,28 @@ def test_argument_errors_are_reported():
     from sparseflow_b200._lib import SfbError
     with pytest.raises(SfbError):
         ops.sparse_gemm(torch.zeros(4, 96, device="cuda", dtype=torch.bfloat16), cw2)
+
+
+def test_random_shapes_through_the_dispatcher():
+    """Seeded random (tokens, rows, K) triples, ragged in every dimension the library allows (rows % 8 == 0,
+    K % 64 == 0), through whatever kernel the dispatcher picks, against an fp32 matmul on the decompressed
+    weight (GPU reference: the decompression itself is pinned bit-exactly elsewhere)."""
+    from sparseflow_b200 import _lib
+    rng = np.random.default_rng(2024)
+    seen = set()
+    for case in range(48):
+        M = int(rng.choice([1, 2, 3, 5, 8, 9, 17, 31, 33, 64, 65, 100, 129, 200, 257, 384, 513, 700, 1023, 1024, 1500]))
+        N = int(rng.choice([8, 24, 120, 128, 136, 392, 512, 1000, 2048, 4096, 4104]))
+        K = int(rng.choice([64, 128, 192, 576, 1024, 1088, 2048, 4160]))
+        seen.add(_lib.lib().sfb200_debug_plan_gemm(M, N, K, 0, 148))
+        g = torch.Generator(device="cuda").manual_seed(case)
+        w = (torch.randn(N, K, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+        x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+        cw = ops.compress_weight(w)
+        y = ops.sparse_gemm(x, cw).float()
+        ref = x.float() @ ops.decompress_24(cw).float().t()
+        floor = 1e-2 * ref.pow(2).mean().sqrt()
+        rel = ((y - ref).abs() / torch.maximum(ref.abs(), floor)).max().item()
+        assert y.shape == (M, N) and rel <= REL_TOL, (M, N, K, rel)
+    assert ops.device_status() == 0
+    assert len(seen) >= 6, seen        # decode, single-CTA tiles, split-K and pair variants were all exercised
