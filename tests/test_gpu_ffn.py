@@ -316,3 +316,40 @@ def test_linear_level_surgery_mlp_and_attention():
     assert b1.mlp.gate_proj._sparse_count == 1
     assert (got_g.float() - want_g.float()).abs().max() <= 1e-2 * want_g.float().abs().max()
     assert ops.device_status() == 0
+
+
+def test_random_ffn_shapes_through_the_c_abi():
+    """Seeded random (tokens, hidden, intermediate) triples through sfb200_ffn_forward (whatever kernels the
+    dispatcher picks for each GEMM) against fp32 math on the decompressed weights with the same rounding points
+    (hidden stored in the 16-bit type)."""
+    import ctypes as C
+    from sparseflow_b200 import _lib
+    rng = np.random.default_rng(7)
+    L = _lib.lib()
+    for case in range(24):
+        M = int(rng.choice([1, 3, 8, 20, 64, 100, 130, 300, 512, 1025, 1400]))
+        H = int(rng.choice([64, 256, 320, 1024, 2048]))
+        I = int(rng.choice([64, 192, 1408, 2752, 4096]))      # I % 64 == 0: it is the K of the down GEMM
+        g = torch.Generator(device="cuda").manual_seed(100 + case)
+        rnd = lambda *s, sigma: (torch.randn(*s, generator=g, device="cuda") * sigma).to(torch.bfloat16)
+        wg, wu, wd, x = rnd(I, H, sigma=0.05), rnd(I, H, sigma=0.05), rnd(H, I, sigma=0.05), rnd(M, H, sigma=1.0)
+        gu, dn = ops.compress_gate_up(wg, wu), ops.compress_weight(wd)
+        W = _lib.FFNWeights(H, I, ops.BF16, gu.values.data_ptr(), gu.meta.data_ptr(), dn.values.data_ptr(),
+                            dn.meta.data_ptr(), None)
+        hid = torch.empty(M, I, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, H, device="cuda", dtype=torch.bfloat16)
+        rc = L.sfb200_ffn_forward(C.byref(W), x.data_ptr(), H, hid.data_ptr(), out.data_ptr(), H, M,
+                                  torch.cuda.current_stream().cuda_stream)
+        assert rc == 0, (M, H, I, rc)
+        pg = ops.prune_compress_24(wg, want_values=False, want_meta=False, want_pruned=True)["pruned"].float()
+        pu = ops.prune_compress_24(wu, want_values=False, want_meta=False, want_pruned=True)["pruned"].float()
+        gg, uu = x.float() @ pg.t(), x.float() @ pu.t()
+        h_ref = (gg * torch.sigmoid(gg) * uu)
+        rms_h = h_ref.pow(2).mean().sqrt()
+        rel_h = ((hid.float() - h_ref).abs() / torch.maximum(h_ref.abs(), 1e-2 * rms_h)).max().item()
+        assert rel_h <= REL_TOL, (M, H, I, "hidden", rel_h)
+        o_ref = hid.float() @ ops.decompress_24(dn).float().t()          # down GEMM on the GPU's own hidden bits
+        rms_o = o_ref.pow(2).mean().sqrt()
+        rel_o = ((out.float() - o_ref).abs() / torch.maximum(o_ref.abs(), 1e-2 * rms_o)).max().item()
+        assert rel_o <= REL_TOL, (M, H, I, "out", rel_o)
+    assert ops.device_status() == 0
