@@ -53,6 +53,7 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama7b_ffn", choices=sorted(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=0, help="override the token count")
+    ap.add_argument("--tp-phases", action="store_true", help="N > 1, fused path: print per-phase device times to stderr")
     ap.add_argument("--chunks", type=int, default=1, help="token chunks for all-reduce overlap (N > 1, --tp nccl)")
     ap.add_argument("--tp", default="fused", choices=["fused", "nccl"],
                     help="N > 1: exchange step fused into the kernels over peer memory, or NCCL all-reduce")
@@ -367,13 +368,23 @@ def main():
     s1.record()
     barrier()
     clocks = sampler.stop()
+    launches = ffn.kernel_launches - launches0
+    if fused_tp and args.tp_phases:       # after the timed region: ten more steps with events between the phases
+        names = ["gate_up_gemm", "down_gemm_scatter", "barrier_1", "reduce_allgather", "barrier_2"]
+        acc = [0.0] * 5
+        for _ in range(10):
+            evs = []
+            ffn.forward(x, phase_events=evs)
+            torch.cuda.synchronize()
+            for i in range(5):
+                acc[i] += evs[i].elapsed_time(evs[i + 1]) / 10
+        sys.stderr.write(f"rank {rank} phases (ms): " + ", ".join(f"{n} {t:.4f}" for n, t in zip(names, acc)) + "\n")
     ops.device_status()
     ms_total = s0.elapsed_time(s1)
     tmax = torch.tensor([ms_total], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
     ms_step = float(tmax.item()) / args.steps
-    launches = ffn.kernel_launches - launches0
     flops = 6.0 * M * H * I
     value = flops / (ms_step * 1e-3) / 1e12
 

@@ -155,7 +155,9 @@ class FusedTensorParallelFFN:
         self.hidden = torch.empty((max_tokens, self.Ip), dtype=self.dtype, device=dev)
         self.kernel_launches = 0
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, phase_events=None) -> torch.Tensor:
+        """``phase_events``: optional list that receives six CUDA events bracketing the five phases of the step
+        (gate|up GEMM, down GEMM + scatter, barrier, reduce + all-gather, barrier) for per-phase timing."""
         from . import _lib
         ops, L, C = self.ops, self.L, self.C
         M = x.shape[0]
@@ -164,15 +166,27 @@ class FusedTensorParallelFFN:
         st = torch.cuda.current_stream().cuda_stream
         dt = ops._dt(x)
         hidden = self.hidden[:M]
+
+        def mark():
+            if phase_events is not None:
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                phase_events.append(e)
+        mark()
         ops.sparse_gemm_swiglu(x, self.gu, out=hidden)
+        mark()
         _lib.check("sfb200_sparse_gemm_scatter", L.sfb200_sparse_gemm_scatter(
             hidden.data_ptr(), hidden.stride(0), self.dn.values.data_ptr(), self.dn.meta.data_ptr(),
             C.cast(self.peer_slots, C.POINTER(C.c_void_p)), self.tp, self.tok_per_owner, M, self.H, self.Ip, dt, st))
+        mark()
         self.h_recv.barrier(channel=0)            # every rank's partial sums have landed
+        mark()
         bias = self.down_bias.data_ptr() if self.down_bias is not None else None
         _lib.check("sfb200_reduce_allgather", L.sfb200_reduce_allgather(
             self.recv.data_ptr(), self.tp, self.tok_per_owner, self.H,
             C.cast(self.peer_out, C.POINTER(C.c_void_p)), dt, bias, st))
+        mark()
         self.h_out.barrier(channel=0)             # every rank's finished block has landed everywhere
+        mark()
         self.kernel_launches += 3
         return self.out[:M]
