@@ -73,7 +73,6 @@ struct Cfg {
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "BN");
   static_assert(TMEM_USED <= 512, "tmem");
   static_assert(SMEM_BYTES <= 232448, "smem");
-  static_assert(BK == 128 || STAGES % 2 == 0 || true, "");
 };
 
 __device__ __forceinline__ float apply_act(float v, int act) {

@@ -454,7 +454,6 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
     const int col0 = (C::RS == 1) ? w2 * C::COLS_PER_WARP : 0;
     const uint32_t leader_acce = mapa_u32(bar_acce, 0);
     const uint64_t pol_stream = l2_policy_evict_first();
-    (void)pol_stream;
     uint32_t aph = 0;
     bool ok = true;
     constexpr int NCH = C::COLS_PER_WARP / 16;
@@ -682,7 +681,6 @@ int dispatch_pair(const SparseGemmArgs& a, cudaStream_t stream) {
   if (v == 0) v = pick_pair_variant_impl(a.n_out, a.m_tok, a.K, a.num_sms / 2);
   switch (v) {
     case 1256: return launch_pair_cfg<PairCfg<256, 128, 4, 1, EPI>>(a, stream);
-    case 1257: return launch_pair_cfg<PairCfg<256, 64, 8, 1, EPI>>(a, stream);   // same tile, 64-wide stages
     case 2192: return launch_pair_cfg<PairCfg<192, 64, 6, 2, EPI>>(a, stream);
     case 2208: return launch_pair_cfg<PairCfg<208, 64, 6, 2, EPI>>(a, stream);
     case 2224: return launch_pair_cfg<PairCfg<224, 64, 6, 2, EPI>>(a, stream);
