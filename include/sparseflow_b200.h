@@ -167,6 +167,11 @@ SFB200_API int sfb200_sparse_gemm_scatter(const void* x, int ldx, const void* va
  */
 SFB200_API int sfb200_reduce_allgather(const void* slots, int tp, int rows, int cols,
                                        void* const* peer_out_blocks, int dtype, const void* bias, void* stream);
+/* Same, for an output tensor that also has a switch-replicated (NVLS) mapping: switch_out_block is this
+ * rank's token block inside that mapping, and every 16-byte result is written with one multimem.st that
+ * NVSwitch delivers to all ranks, so the finished block leaves this GPU once instead of tp - 1 times. */
+SFB200_API int sfb200_reduce_allgather_switch(const void* slots, int tp, int rows, int cols, void* switch_out_block,
+                                              int dtype, const void* bias, void* stream);
 
 /*
  * Gated FFN forward for callers that cannot allocate device memory (no counterpart in the

@@ -74,6 +74,7 @@ def lib() -> C.CDLL:
     L.sfb200_ffn_forward_host.argtypes = [C.POINTER(FFNWeights), vp, vp, i, vp]
     L.sfb200_sparse_gemm_scatter.argtypes = [vp, i, vp, vp, C.POINTER(vp), i, i, i, i, i, i, vp]
     L.sfb200_reduce_allgather.argtypes = [vp, i, i, i, C.POINTER(vp), i, vp, vp]
+    L.sfb200_reduce_allgather_switch.argtypes = [vp, i, i, i, vp, i, vp, vp]
     L.sfb200_ffn_forward_noalloc.argtypes = [C.POINTER(FFNWeights), vp, i, vp, i, i, vp]
     L.sfb200_debug_force_token_tile.argtypes = [i]
     L.sfb200_debug_plan_gemm.argtypes = [i, i, i, i, i]

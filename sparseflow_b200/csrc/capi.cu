@@ -348,7 +348,16 @@ int sfb200_reduce_allgather(const void* slots, int tp, int rows, int cols, void*
   int err = kOk;
   if (!device_state(&err)) return err;
   if (!peer_out_blocks) return kErrInvalid;
-  return launch_reduce_allgather(slots, tp, rows, cols, peer_out_blocks, dtype, bias,
+  return launch_reduce_allgather(slots, tp, rows, cols, peer_out_blocks, nullptr, dtype, bias,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+int sfb200_reduce_allgather_switch(const void* slots, int tp, int rows, int cols, void* switch_out_block, int dtype,
+                                   const void* bias, void* stream) {
+  int err = kOk;
+  if (!device_state(&err)) return err;
+  if (!switch_out_block) return kErrInvalid;
+  return launch_reduce_allgather(slots, tp, rows, cols, nullptr, switch_out_block, dtype, bias,
                                  static_cast<cudaStream_t>(stream));
 }
 

@@ -83,8 +83,10 @@ int launch_sparse_gemm_pair_scatter(const SparseGemmArgs& a, void* const* peer_s
                                     cudaStream_t stream);
 // out_block = sum over tp receive slots (fp32), written to every rank's output at this rank's token
 // block (all-gather fused into the reduction).  slots: [tp][rows, cols] contiguous, local.
-int launch_reduce_allgather(const void* slots, int tp, int rows, int cols, void* const* peer_out_blocks, int fmt,
-                            const void* bias, cudaStream_t stream);
+// switch_out_block != null: this rank's block inside the switch-replicated mapping of the output (one multimem
+// store reaches every rank) and peer_out_blocks is ignored.
+int launch_reduce_allgather(const void* slots, int tp, int rows, int cols, void* const* peer_out_blocks,
+                            void* switch_out_block, int fmt, const void* bias, cudaStream_t stream);
 
 // Split-K variant of the single-CTA kernel: a cluster of `split` (2 or 4) CTAs shares one output tile,
 // each streaming a slice of K; partial tiles are reduced through distributed shared memory.  Chosen by

@@ -119,7 +119,7 @@ class FusedTensorParallelFFN:
     """TP FFN whose exchange step is fused into the kernels (peer stores over NVLink)."""
 
     def __init__(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, max_tokens: int, group=None,
-                 down_bias: Optional[torch.Tensor] = None):
+                 down_bias: Optional[torch.Tensor] = None, use_switch_stores: bool = True):
         import ctypes as C
         import torch.distributed._symmetric_memory as symm_mem
         from . import _lib, ops
@@ -152,6 +152,10 @@ class FusedTensorParallelFFN:
         # rank o's slot for my partial sums; rank d's output rows of my token block
         self.peer_slots = VP(*[(recv_ptrs[o] + self.rank * blk) if o < self.tp else None for o in range(8)])
         self.peer_out = VP(*[(out_ptrs[d] + self.rank * blk) if d < self.tp else None for d in range(8)])
+        # NVSwitch-replicated mapping of the output, when the fabric offers one: the all-gather then sends each
+        # finished block once (multimem.st) instead of once per peer
+        mc = int(getattr(self.h_out, "multicast_ptr", 0) or 0) if use_switch_stores else 0
+        self.switch_out = (mc + self.rank * blk) if mc else 0
         self.hidden = torch.empty((max_tokens, self.Ip), dtype=self.dtype, device=dev)
         self.kernel_launches = 0
 
@@ -182,9 +186,13 @@ class FusedTensorParallelFFN:
         self.h_recv.barrier(channel=0)            # every rank's partial sums have landed
         mark()
         bias = self.down_bias.data_ptr() if self.down_bias is not None else None
-        _lib.check("sfb200_reduce_allgather", L.sfb200_reduce_allgather(
-            self.recv.data_ptr(), self.tp, self.tok_per_owner, self.H,
-            C.cast(self.peer_out, C.POINTER(C.c_void_p)), dt, bias, st))
+        if self.switch_out:
+            _lib.check("sfb200_reduce_allgather_switch", L.sfb200_reduce_allgather_switch(
+                self.recv.data_ptr(), self.tp, self.tok_per_owner, self.H, self.switch_out, dt, bias, st))
+        else:
+            _lib.check("sfb200_reduce_allgather", L.sfb200_reduce_allgather(
+                self.recv.data_ptr(), self.tp, self.tok_per_owner, self.H,
+                C.cast(self.peer_out, C.POINTER(C.c_void_p)), dt, bias, st))
         mark()
         self.h_out.barrier(channel=0)             # every rank's finished block has landed everywhere
         mark()

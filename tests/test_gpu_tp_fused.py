@@ -34,13 +34,16 @@ def _worker(rank, world, port, ret):
         wg, wu, wd = seeded((I, H), 1, 0.02), seeded((I, H), 2, 0.02), seeded((H, I), 3, 0.02)
         x = seeded((M, H), 4, 1.0)
         ref = parallel.TensorParallelFFN(wg, wu, wd).forward(x).clone()
-        fused = parallel.FusedTensorParallelFFN(wg, wu, wd, max_tokens=M)
+        fused = parallel.FusedTensorParallelFFN(wg, wu, wd, max_tokens=M)             # switch stores if the fabric has them
         a = fused.forward(x).clone()
         b = fused.forward(x).clone()
+        plain = parallel.FusedTensorParallelFFN(wg, wu, wd, max_tokens=M, use_switch_stores=False)
+        c = plain.forward(x).clone()
         torch.cuda.synchronize()
-        assert ops.device_status() == 0
+        assert ops.device_status() == 0 and plain.switch_out == 0
         err = (a.float() - ref.float()).abs().max().item()
-        ret[rank] = (err <= 2.0 ** -7 * ref.float().abs().max().item(), torch.equal(a, b))
+        ret[rank] = (err <= 2.0 ** -7 * ref.float().abs().max().item(), torch.equal(a, b) and torch.equal(a, c))
+        ret[f"switch{rank}"] = bool(fused.switch_out)
     finally:
         dist.destroy_process_group()
 
@@ -53,4 +56,6 @@ def test_fused_tp_matches_nccl_two_gpus():
     with mp.Manager() as mgr:
         ret = mgr.dict()
         mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
-        assert dict(ret) == {0: (True, True), 1: (True, True)}
+        got = dict(ret)
+        print("switch-replicated output mapping in use:", got.pop("switch0"), got.pop("switch1"))
+        assert got == {0: (True, True), 1: (True, True)}
