@@ -53,6 +53,7 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama7b_ffn", choices=sorted(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=0, help="override the token count")
+    ap.add_argument("--tp-switch", action="store_true", help="N > 1, fused path: all-gather through NVSwitch-replicated stores")
     ap.add_argument("--tp-phases", action="store_true", help="N > 1, fused path: print per-phase device times to stderr")
     ap.add_argument("--chunks", type=int, default=1, help="token chunks for all-reduce overlap (N > 1, --tp nccl)")
     ap.add_argument("--tp", default="fused", choices=["fused", "nccl"],
@@ -312,7 +313,7 @@ def main():
     ffn = None
     if world > 1 and args.tp == "fused":
         try:
-            ffn = parallel.FusedTensorParallelFFN(wg, wu, wd, max_tokens=M)
+            ffn = parallel.FusedTensorParallelFFN(wg, wu, wd, max_tokens=M, use_switch_stores=args.tp_switch)
             tp_mode = "fused: reduce-scatter in the down-GEMM epilogue (TMA stores to peer memory), all-gather in the reduction kernel"
         except Exception as exc:      # symmetric memory unavailable on this box: NCCL path
             sys.stderr.write(f"fused tensor-parallel path unavailable ({exc!r}); using NCCL all-reduce\n")

@@ -34,10 +34,10 @@ def _worker(rank, world, port, ret):
         wg, wu, wd = seeded((I, H), 1, 0.02), seeded((I, H), 2, 0.02), seeded((H, I), 3, 0.02)
         x = seeded((M, H), 4, 1.0)
         ref = parallel.TensorParallelFFN(wg, wu, wd).forward(x).clone()
-        fused = parallel.FusedTensorParallelFFN(wg, wu, wd, max_tokens=M)             # switch stores if the fabric has them
+        fused = parallel.FusedTensorParallelFFN(wg, wu, wd, max_tokens=M, use_switch_stores=True)   # if the fabric has them
         a = fused.forward(x).clone()
         b = fused.forward(x).clone()
-        plain = parallel.FusedTensorParallelFFN(wg, wu, wd, max_tokens=M, use_switch_stores=False)
+        plain = parallel.FusedTensorParallelFFN(wg, wu, wd, max_tokens=M)
         c = plain.forward(x).clone()
         torch.cuda.synchronize()
         assert ops.device_status() == 0 and plain.switch_out == 0
