@@ -408,10 +408,23 @@ int plan_sparse_gemm(int m_tok, int n_out, int K, int epi, int num_sms) {
   // kernel it only wins at 1-2 tokens when both apply
   if (m_tok <= kSmallMMaxTokens && (split == 1 || m_tok <= 2)) return 8;
   if (m_tok >= kPairMinTokens) return pick_pair_variant(n_out, m_tok, K, num_sms);
+  if (m_tok > 64 && m_tok <= 128) {
+    // 65..128 tokens: one 128-token tile per row tile, two 64-token tiles, or split K.  A 128-wide stage of the
+    // 128-token tile holds 50 KB and is feed-bound (~430 ns), of the 64-token tile 34 KB (~268 ns); what decides is
+    // again the number of passes over the SMs.  (Measured: 8192 x 8192 at 128 tokens 27.9 -> 20.5 us with two
+    // 64-token tiles; 22016 x 4096 31.6 -> 28.9 us; 11008 x 4096 and 28672 x 4096 stay with the 128-token tile.)
+    const long mb = (n_out + 127) / 128;
+    const double k128 = (K + 127) / 128;
+    auto waves = [&](long tiles) { return static_cast<double>((tiles + num_sms - 1) / num_sms); };
+    const double c128 = waves(mb) * k128 * 430e-9 + 4e-6;
+    const double c64 = waves(2 * mb) * k128 * 268e-9 + 4e-6;
+    const double csplit = split > 1 ? (k128 / split) * 385e-9 + 10e-6 : 1e30;
+    if (epi == kEpiStore && csplit < c128 && csplit < c64) return (split == 4 ? 4000 : 3000) + 128;
+    return c64 < c128 ? 64 : 128;
+  }
   if (split > 1) return (split == 4 ? 4000 : 3000) + splitk_token_tile(m_tok);
   if (m_tok <= 32) return 32;
   if (m_tok <= 64) return 64;
-  if (m_tok <= 128) return 128;
   return pick_mid_variant(n_out, m_tok, K, num_sms);
 }
 

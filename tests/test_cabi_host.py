@@ -188,12 +188,14 @@ def test_kernel_plan_per_shape():
     assert plan(5, 28672, 4096) == 32 and plan(8, 22016, 4096, 1) == 32
     assert plan(2, 4096, 14336) == 8 and plan(4, 4096, 14336) == 4032
     # few row tiles, below the prefill threshold: split-K over a cluster, 4 slices for 32 tiles, 2 for 64
-    assert plan(32, 4096, 11008) == 4032 and plan(64, 4096, 11008) == 4064 and plan(128, 4096, 4096) == 4128
+    assert plan(32, 4096, 11008) == 4032 and plan(64, 4096, 11008) == 4064 and plan(128, 4096, 11008) == 4128
     assert plan(16, 8192, 8192) == 3032 and plan(64, 8192, 8192) == 3064
-    assert plan(128, 8192, 8192) == 128               # two slices of a 128-token tile do not pay
+    # 65..128 tokens: two 64-token tiles where they need no more passes over the SMs than one 128-token tile
+    assert plan(128, 8192, 8192) == 64 and plan(128, 4096, 4096) == 64 and plan(128, 22016, 4096) == 64
+    assert plan(128, 11008, 4096) == 128 and plan(100, 28672, 4096) == 128
     assert plan(32, 512, 256) == 32                   # too little K to split (< 4 metadata tiles per slice)
     # many row tiles, up to 128 tokens: single-CTA kernel with the smallest covering token tile
-    assert plan(9, 22016, 4096) == 32 and plan(33, 22016, 4096) == 64 and plan(100, 22016, 4096) == 128
+    assert plan(9, 22016, 4096) == 32 and plan(33, 22016, 4096) == 64 and plan(100, 11008, 4096) == 128
     assert plan(64, 22016, 4096, 1) == 64             # the SwiGLU epilogue has no split-K form
     # 129..1023 tokens: cost model over tile waves
     assert plan(512, 14336, 4096) == 1256 and plan(512, 22016, 4096, 1) == 1256
