@@ -168,7 +168,7 @@ class FusedTensorParallelFFN:
         M = x.shape[0]
         if M > self.max_tokens:
             raise ValueError(f"{M} tokens exceed the {self.max_tokens} this instance was built for")
-        st = torch.cuda.current_stream().cuda_stream
+        st = ops._stream()
         dt = ops._dt(x)
         hidden = self.hidden[:M]
 
