@@ -153,8 +153,8 @@ class FusedTensorParallelFFN:
         self.peer_slots = VP(*[(recv_ptrs[o] + self.rank * blk) if o < self.tp else None for o in range(8)])
         self.peer_out = VP(*[(out_ptrs[d] + self.rank * blk) if d < self.tp else None for d in range(8)])
         # Optional: NVSwitch-replicated mapping of the output, when the fabric offers one; the all-gather then sends
-        # each finished block once (multimem.st) instead of once per peer.  Off by default: at 2 ranks, where it
-        # saves no traffic, the 16-byte switch stores measured slower than plain peer stores (0.059 vs 0.037 ms).
+        # each finished block once (multimem.st) instead of once per peer.  Off by default: the 16-byte switch
+        # stores measured slower than plain peer stores at 2 ranks (0.059 vs 0.037 ms) and at 4 (0.057 vs 0.051 ms).
         mc = int(getattr(self.h_out, "multicast_ptr", 0) or 0) if use_switch_stores else 0
         self.switch_out = (mc + self.rank * blk) if mc else 0
         self.hidden = torch.empty((max_tokens, self.Ip), dtype=self.dtype, device=dev)
