@@ -7,12 +7,18 @@
 One step = one forward of the gated FFN  out = down(silu(gate(x)) * up(x))  over one batch of
 synthetic tokens, both GEMMs 2:4-sparse.  Default workload: Llama-7B shapes (hidden 4096,
 intermediate 11008), 4096 prefill tokens, bf16, weights N(0, 0.02) pruned 2:4, x ~ N(0, 1), seeded.
-With N > 1 the same FFN is tensor-parallel (column-parallel gate/up, row-parallel down, NCCL
-all-reduce): total work fixed, "scaling": "strong".
+With N > 1 the same FFN is tensor-parallel (column-parallel gate/up, row-parallel down, one exchange
+step): total work fixed, "scaling": "strong".
 
 Prints ONE JSON line (rank 0).  `value` is dense-equivalent TFLOP/s (6*M*H*I / t) with inputs
-resident in HBM; `e2e` is the same metric through the host-buffer C-ABI call, with the host->device
-copy of x and the device->host copy of the result inside the timed region.
+resident in HBM; `e2e` is the same metric with host buffers: the host->device copy of x and the
+device->host copy of the result are inside the timed region.  `parity` compares the step's output
+with the CPU oracle (the reference's CPU path) after the timed region; a failed comparison makes
+the process exit non-zero.
+
+Other modes (each prints its own small report, not the benchmark line):
+    --only {prune,gate_up,down,decode}   a few launches of one kernel (what a profiler capture runs)
+    --sweep {gemm,ffn}                   the standalone-GEMM shape grid / the gated-FFN token sweep
 """
 from __future__ import annotations
 
@@ -36,13 +42,11 @@ WORKLOADS = {
     "llama70b_ffn": (8192, 28672, 8192),
 }
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate|up kernel, from the ncu
-# capture summarised in profiles/ (None until a capture of that workload exists).
-NCU_TRAFFIC_BYTES = {
-    # profiles/sparse_gemm_pair_gate_up_llama7b.md: 149.2 MB measured at M = 2048, scaled to M = 4096
-    # (weights fixed, activations and outputs proportional to M)
-    "llama7b_ffn": 196.2e6,
-}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the gate|up kernel from a profiler capture at
+# 2048 tokens (149.2 MB), scaled to 4096 tokens: weights fixed, activations and outputs proportional to tokens.
+NCU_TRAFFIC_BYTES = {"llama7b_ffn": 196.2e6}
+
+PARITY_TOL = 1e-2      # FFN output: |d| <= tol * max(|ref|, rms(ref)) and max|d| <= tol * max|ref|
 
 
 def parse_args():
@@ -53,31 +57,43 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama7b_ffn", choices=sorted(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=0, help="override the token count")
-    ap.add_argument("--tp-switch", action="store_true", help="N > 1, fused path: all-gather through NVSwitch-replicated stores")
-    ap.add_argument("--tp-phases", action="store_true", help="N > 1, fused path: print per-phase device times to stderr")
+    ap.add_argument("--tp", default="fused", choices=["fused", "scatter", "nccl"],
+                    help="N > 1: exchange step in one kernel through NVSwitch (fused), scatter epilogue + reduce kernel "
+                         "over peer stores (scatter), or NCCL all-reduce (nccl)")
+    ap.add_argument("--tp-phases", action="store_true", help="N > 1: print per-phase device times to stderr")
     ap.add_argument("--chunks", type=int, default=1, help="token chunks for all-reduce overlap (N > 1, --tp nccl)")
-    ap.add_argument("--tp", default="fused", choices=["fused", "nccl"],
-                    help="N > 1: exchange step fused into the kernels over peer memory, or NCCL all-reduce")
-    ap.add_argument("--cpu-tokens", type=int, default=0, help="tokens of the CPU baseline sample (0 = auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle comparison (it prunes the weights on the CPU)")
+    ap.add_argument("--parity-tokens", type=int, default=0, help="rows of the output compared with the oracle (0 = all, 1024 for the 70B shapes)")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the 2 x 2 s sustained-clock loops")
+    ap.add_argument("--only", default=None, choices=["prune", "gate_up", "down", "decode"],
+                    help="run a few launches of one kernel and exit")
+    ap.add_argument("--iters", type=int, default=2, help="--only: launches after the warm-up launch")
+    ap.add_argument("--tile", type=int, default=0, help="--only / main run: kernel variant override (0 = automatic)")
+    ap.add_argument("--tile-down", type=int, default=0, help="main run: variant override of the down GEMM only")
+    ap.add_argument("--hidden", type=int, default=0)
+    ap.add_argument("--inter", type=int, default=0)
+    ap.add_argument("--sweep", default=None, choices=["gemm", "ffn"])
+    ap.add_argument("--json", default=None, help="--sweep: also write the rows to this file")
     return ap.parse_args()
 
 
 # ------------------------------------------------------------------------------------------------
 # clocks
 class ClockSampler:
-    """Samples SM clock and throttle reasons while the timed region runs (read-only NVML queries,
-    every 2 ms; falls back to polling nvidia-smi when the NVML binding is missing)."""
+    """Samples SM clock, power and throttle reasons (read-only NVML queries; falls back to polling nvidia-smi
+    when the NVML binding is missing).  Runs from before the warm-up to the end of the run; `summary(t0, t1)` is
+    computed over the samples that fall inside a region."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    BITS = (("hw_slowdown", 0x8), ("sw_power_cap", 0x4), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40))
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, interval_s: float = 0.001):
         self.index = index
-        self.sm = []
-        self.power = []
+        self.interval = interval_s
+        self.samples = []        # (t, sm_mhz, power_w or None, reasons bitmask)
         self.max_sm = 0.0
-        self.reasons = set()
         self._stop = threading.Event()
         self._t = None
         self._nvml = None
@@ -87,6 +103,8 @@ class ClockSampler:
             self._h = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index(index))
             self._nvml = pynvml
             self.max_sm = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+            self._reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
         except Exception:
             self._nvml = None
 
@@ -100,54 +118,74 @@ class ClockSampler:
                 return index
         return index
 
-    def _sample_nvml(self):
+    def _sample_nvml(self, k: int):
         n = self._nvml
-        self.sm.append(float(n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM)))
+        sm = float(n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM))
+        t = time.perf_counter()
+        power, reasons = None, 0
         try:
-            self.power.append(n.nvmlDeviceGetPowerUsage(self._h) / 1000.0)
+            reasons = int(self._reasons(self._h))
+            if k % 4 == 0:
+                power = n.nvmlDeviceGetPowerUsage(self._h) / 1000.0
         except Exception:
             pass
-        r = n.nvmlDeviceGetCurrentClocksEventReasons(self._h) if hasattr(n, "nvmlDeviceGetCurrentClocksEventReasons") \
-            else n.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
-        for name, bit in (("hw_slowdown", 0x8), ("sw_power_cap", 0x4), ("sw_thermal_slowdown", 0x20),
-                          ("hw_thermal_slowdown", 0x40)):
-            if r & bit:
-                self.reasons.add(name)
+        self.samples.append((t, sm, power, reasons))
 
     def _sample_smi(self):
         out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                               "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
         f = [v.strip() for v in out.strip().split(",")]
         if len(f) >= 7:
-            self.sm.append(float(f[0]))
             self.max_sm = max(self.max_sm, float(f[1]))
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
+            mask = 0
+            for (name, bit), v in zip((("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+                                       ("sw_power_cap", 0x4)), f[3:7]):
                 if v.lower().startswith("active"):
-                    self.reasons.add(name)
+                    mask |= bit
+            try:
+                power = float(f[2])
+            except ValueError:
+                power = None
+            self.samples.append((time.perf_counter(), float(f[0]), power, mask))
 
     def _run(self):
+        k = 0
         while not self._stop.is_set():
             try:
                 if self._nvml is not None:
-                    self._sample_nvml()
+                    self._sample_nvml(k)
                 else:
                     self._sample_smi()
             except Exception:
                 pass
-            self._stop.wait(0.002)
+            k += 1
+            self._stop.wait(self.interval)
 
     def start(self):
         self._t = threading.Thread(target=self._run, daemon=True)
         self._t.start()
 
-    def stop(self) -> dict:
+    def stop(self):
         self._stop.set()
         if self._t:
             self._t.join(timeout=6)
-        sm = sorted(self.sm)
+
+    def summary(self, t0: float, t1: float) -> dict:
+        """Over the samples taken in [t0, t1] (perf_counter times); when the region is shorter than the sampling
+        period allows (fewer than 3 samples) the window is widened by 20 ms on both sides, and says so."""
+        inside = [s for s in self.samples if t0 <= s[0] <= t1]
+        widened = False
+        if len(inside) < 3:
+            inside = [s for s in self.samples if t0 - 0.02 <= s[0] <= t1 + 0.02]
+            widened = True
+        sm = sorted(s[1] for s in inside)
+        power = [s[2] for s in inside if s[2] is not None]
+        mask = 0
+        for s in inside:
+            mask |= s[3]
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.max_sm or None,
-                "reasons": sorted(self.reasons), "samples": len(sm),
-                "power_w_max": max(self.power) if self.power else None,
+                "reasons": sorted(name for name, bit in self.BITS if mask & bit), "samples": len(sm),
+                "power_w_max": max(power) if power else None, "window_widened_20ms": widened,
                 "source": "nvml" if self._nvml is not None else "nvidia-smi"}
 
 
@@ -161,68 +199,100 @@ def measured_peaks():
         return 1590.0, 1400.0, 6650.0, "fallback"
 
 
-def cpu_reference_ffn(H, I, tokens, threads, reps=1):
-    """The reference's CPU path on a sample of `tokens` tokens: oracle pruning of seeded weights is
-    done once outside the timing (weights are pruned at load time in both arms); timed: the
-    fp32-accumulated gated FFN on the pruned weights, all host threads."""
-    import numpy as np
+def workload_dims(args):
+    H, I, M = WORKLOADS[args.workload]
+    if args.hidden:
+        H = args.hidden
+    if args.inter:
+        I = args.inter
+    if args.tokens:
+        M = args.tokens
+    return H, I, M
+
+
+def config_dict(args, H, I, M) -> dict:
+    """The same dictionary from both arms (ours and --impl reference) for the same command line."""
+    n = max(1, args.gpus)
+    return {"workload": f"{args.workload}: hidden {H}, intermediate {I}, {M} tokens, bf16, 2:4-pruned gate/up/down",
+            "hidden": H, "intermediate": I, "tokens": M,
+            "parallelism": "single GPU" if n == 1 else f"tp{n}: column-parallel gate/up, row-parallel down, one exchange step",
+            "l2": "no flush: per-step working set (weights 152 MB + activations 157 MB for the default workload) exceeds the 126 MB L2"}
+
+
+def seeded_cpu(shape, seed, sigma):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g, dtype=torch.float32) * sigma).to(torch.bfloat16)
+
+
+_ORACLE_W = {}
+
+
+def oracle_pruned_weights(H, I):
+    """The three weights of the workload pruned by the CPU oracle (the reference's prune_24_cpu rule), as fp32
+    torch tensors.  Cached: parity check, CPU baseline and the reference arm share them."""
     import torch
     import oracle as o
-    torch.set_num_threads(threads)
-    g = torch.Generator().manual_seed(1)
-    ws = []
-    for shape, seed in (((I, H), 1), ((I, H), 2), ((H, I), 3)):
-        gen = torch.Generator().manual_seed(seed)
-        w = (torch.randn(shape, generator=gen) * 0.02).numpy()
-        ws.append(torch.from_numpy(o.to_f32(o.prune_24_pruned_chunked(o.from_f32(w, "bf16"), "bf16"), "bf16")))
-    x = torch.randn(tokens, H, generator=g).bfloat16().float()
-    wg, wu, wd = ws
-
-    def step():
-        gt = (x @ wg.T)
-        ut = (x @ wu.T)
-        h = (torch.nn.functional.silu(gt) * ut).bfloat16().float()
-        return (h @ wd.T).bfloat16()
-
-    step()
-    best = float("inf")
-    for _ in range(reps):
-        t0 = time.perf_counter()
-        step()
-        best = min(best, time.perf_counter() - t0)
-    return best
+    key = (H, I)
+    if key not in _ORACLE_W:
+        ws = []
+        for shape, seed in (((I, H), 1), ((I, H), 2), ((H, I), 3)):
+            bits = seeded_cpu(shape, seed, 0.02).view(torch.int16).numpy().view("uint16")
+            ws.append(torch.from_numpy(o.to_f32(o.prune_24_pruned_chunked(bits, "bf16"), "bf16")))
+        _ORACLE_W[key] = ws
+    return _ORACLE_W[key]
 
 
-def pick_cpu_tokens(H, I, threads, want_seconds=3.0):
-    # assume ~15 GFLOP/s per thread for fp32 sgemm; clamp to [64, 1024]
-    flops_per_tok = 6.0 * H * I
-    toks = int(want_seconds * threads * 15e9 / flops_per_tok)
-    return max(64, min(1024, (toks // 64) * 64))
+def oracle_ffn(x_bf16_cpu, H, I):
+    """The reference's CPU path on pruned weights: fp32-accumulated matmuls (experiments/gen_pruned_ref.py:5-8),
+    SiLU.mul in fp32, hidden rounded to bf16 (the dataflow of a fused epilogue); returns the fp32 output."""
+    import torch
+    wg, wu, wd = oracle_pruned_weights(H, I)
+    x = x_bf16_cpu.float()
+    h = (torch.nn.functional.silu(x @ wg.T) * (x @ wu.T)).bfloat16().float()
+    return h @ wd.T
+
+
+def parity_object(out_dev, x_host, H, I, rows) -> dict:
+    """Compare out[:rows] (device, bf16) with the oracle; the four error definitions in use for this path."""
+    import oracle as o
+    ref = oracle_ffn(x_host[:rows], H, I).numpy()
+    got = out_dev[:rows].float().cpu().numpy()
+    m = o.rel_err_metrics(got, ref)
+    ok = bool(m["chain"] <= PARITY_TOL and m["norm"] <= PARITY_TOL)
+    return {"ok": ok, "rows_checked": rows, "tolerance": PARITY_TOL,
+            "bound": "chain <= tol and norm <= tol (chain: |d| / max(|ref|, rms); norm: max|d| / max|ref|)",
+            "chain": m["chain"], "norm": m["norm"], "floor": m["floor"], "eps": m["eps"], "max_abs": m["max_abs"],
+            "oracle": "CPU: oracle 2:4 pruning + fp32 matmuls on the pruned weights (torch CPU sgemm), hidden rounded to bf16"}
 
 
 def run_reference_arm(args):
-    """`--impl reference`: the reference's CPU path (oracle port) timed on the host cores."""
+    """`--impl reference`: the reference's CPU path (oracle port) timed on the host cores, full token count,
+    --steps / --warmup honoured (rank 0 only under torchrun)."""
+    import torch
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    H, I, M = WORKLOADS[args.workload]
-    if args.tokens:
-        M = args.tokens
+    H, I, M = workload_dims(args)
     threads = os.cpu_count() or 1
-    toks = args.cpu_tokens or pick_cpu_tokens(H, I, threads)
-    steps = max(1, min(args.steps, 5))
-    warm = 1
-    t = cpu_reference_ffn(H, I, toks, threads, reps=steps)     # one untimed warm-up step inside
-    tflops = 6.0 * toks * H * I / t / 1e12
+    torch.set_num_threads(threads)
+    x = seeded_cpu((M, H), 1234, 1.0)
+    oracle_pruned_weights(H, I)                      # pruned once at load time, as in the GPU arm
+    warm = max(1, args.warmup)
+    for _ in range(warm):
+        oracle_ffn(x, H, I)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle_ffn(x, H, I).bfloat16()
+    t = (time.perf_counter() - t0) / args.steps
+    tflops = 6.0 * M * H * I / t / 1e12
     line = {
         "impl": "reference", "metric": "dense_equiv_tflops_gated_ffn", "value": tflops, "unit": "TFLOP/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": t * 1e3 * (M / toks),
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": warm, "ms_per_step": t * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic",
-        "config": {"workload": f"{args.workload}: hidden {H}, intermediate {I}, {M} tokens, bf16, 2:4-pruned gate/up/down",
-                   "hidden": H, "intermediate": I, "tokens": M},
+        "data": "synthetic", "config": config_dict(args, H, I, M),
         "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-                         "sample": f"{toks} of {M} tokens, fp32 matmul on oracle-pruned weights, torch CPU, best of {steps}"},
+                         "sample": f"all {M} tokens per step, fp32 matmul on oracle-pruned weights, torch CPU, mean of {args.steps} steps"},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -242,19 +312,180 @@ def _p50_p95(xs):
     return [xs[len(xs) // 2], xs[min(len(xs) - 1, int(round(0.95 * (len(xs) - 1))))]]
 
 
+def run_only(args):
+    """A warm-up launch plus --iters launches of ONE kernel on seeded inputs (Llama-7B shapes unless --hidden /
+    --inter say otherwise): gate_up = fused gate|up GEMM with SiLU.mul epilogue (2*inter x hidden weight),
+    down = hidden x inter weight, prune = prune+compress of the inter x hidden gate weight, decode = the down
+    case at a few tokens.  This is what the profiler captures under profiles/ run."""
+    import torch
+    from sparseflow_b200 import ops
+    dev = torch.device("cuda:0")
+    H, I, M = workload_dims(args)
+    if args.only == "decode" and not args.tokens:
+        M = 8
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def rnd(*s, sigma=1.0):
+        return (torch.randn(*s, generator=g, device=dev, dtype=torch.float32) * sigma).to(torch.bfloat16)
+    ops.force_token_tile(args.tile)
+    if args.only == "prune":
+        w = rnd(I, H, sigma=0.02)
+        vals = torch.empty(I, H // 2, device=dev, dtype=torch.bfloat16)
+        from sparseflow_b200 import _lib
+        meta = torch.empty(_lib.lib().sfb200_meta_bytes(I, H), device=dev, dtype=torch.uint8)
+
+        def fn():
+            _lib.check("prune", _lib.lib().sfb200_prune_compress_24(w.data_ptr(), I, H, H, ops.BF16, 0, vals.data_ptr(),
+                                                                    meta.data_ptr(), None, None, ops._stream()))
+        work = f"{I * H * 3.125 / 1e6:.1f} MB algorithmic"
+    elif args.only == "gate_up":
+        cw = ops.compress_gate_up(rnd(I, H, sigma=0.02), rnd(I, H, sigma=0.02))
+        x = rnd(M, H)
+        out = torch.empty(M, I, device=dev, dtype=torch.bfloat16)
+        fn = lambda: ops.sparse_gemm_swiglu(x, cw, out=out)
+        work = f"{4.0 * M * I * H / 1e9:.1f} GFLOP dense-equivalent"
+    else:
+        cw = ops.compress_weight(rnd(H, I, sigma=0.02))
+        x = rnd(M, I)
+        out = torch.empty(M, H, device=dev, dtype=torch.bfloat16)
+        fn = lambda: ops.sparse_gemm(x, cw, out=out)
+        work = f"{2.0 * M * I * H / 1e9:.1f} GFLOP dense-equivalent"
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    print(f"{args.only} hidden={H} inter={I} tokens={M} tile={args.tile}: {e0.elapsed_time(e1) / args.iters * 1e3:.1f} us "
+          f"per launch ({work}); device status {ops.device_status()}")
+
+
+def run_sweep(args):
+    """--sweep gemm: standalone GEMM, fp16 and bf16, M in {16,128,1024,4096,16384} x (K,N) in {(4096,4096),
+    (4096,11008),(11008,4096),(8192,8192)}: dense-equivalent TFLOP/s, algorithmic GB/s, speed-up over the library
+    GEMM on the same pruned weight stored dense, and what the shape gate would pick.
+    --sweep ffn: gated-FFN token sweep M in {1,8,32,128,512,2048,8192} (Mistral-7B shapes unless --hidden/--inter):
+    pruned-dense (library GEMMs + SiLU.mul), always-sparse, and gated ("auto").
+    Weights rotate over several copies (> L2 in total); token counts up to 512 are timed as CUDA graphs of 20
+    launches (device time), larger ones eagerly with CUDA events."""
+    import torch
+    import torch.nn as nn
+    import torch.nn.functional as F
+    from sparseflow_b200 import dispatch, ops
+    from sparseflow_b200.fused_mlp import SparseFlowFusedMLP
+    from sparseflow_b200.gate_sweep import _time, _time_graph
+    dev = torch.device("cuda:0")
+    ops.force_token_tile(0)
+
+    def timeit(fn, M):
+        return _time_graph(fn) if M <= 512 else _time(fn, 12)
+    rows = []
+    if args.sweep == "gemm":
+        for dt, name in ((torch.float16, "f16"), (torch.bfloat16, "bf16")):
+            for K, N in [(4096, 4096), (4096, 11008), (11008, 4096), (8192, 8192)]:
+                copies = max(2, min(6, int(400e6 // (N * K * 2)) + 1))
+                g = torch.Generator(device=dev).manual_seed(1)
+                ws = [ops.compress_weight((torch.randn(N, K, device=dev, generator=g) * 0.02).to(dt)) for _ in range(copies)]
+                wd = [ops.decompress_24(c) for c in ws]
+                for M in [16, 128, 1024, 4096, 16384]:
+                    gx = torch.Generator(device=dev).manual_seed(1234)
+                    x = torch.randn(M, K, device=dev, generator=gx).to(dt)
+                    y = torch.empty(M, N, device=dev, dtype=dt)
+                    yd = torch.empty(M, N, device=dev, dtype=dt)
+                    i = [0]
+
+                    def fs():
+                        ops.sparse_gemm(x, ws[i[0] % copies], out=y)
+                        i[0] += 1
+
+                    def fd():
+                        torch.matmul(x, wd[i[0] % copies].t(), out=yd)
+                        i[0] += 1
+                    ts, td = timeit(fs, M), timeit(fd, M)
+                    i[0] = 0
+                    fs()
+                    ref = x.float() @ wd[0].float().t()
+                    err = ((y.float() - ref).abs().max() / ref.abs().max()).item()
+                    byts = N * K * 1.125 + M * K * 2 + M * N * 2
+                    r = dict(dtype=name, K=K, N=N, M=M, sparse_us=ts * 1e3, dense_us=td * 1e3, speedup=td / ts,
+                             sparse_tflops=2.0 * M * N * K / ts / 1e9, dense_tflops=2.0 * M * N * K / td / 1e9,
+                             sparse_gbs=byts / ts / 1e6, max_err_over_max=err,
+                             gate_picks_sparse=dispatch.should_use_sparse(M, K, N))
+                    rows.append(r)
+                    print(f"{name} K={K:5d} N={N:5d} M={M:5d}: sparse {r['sparse_us']:8.1f} us {r['sparse_tflops']:7.1f} TF "
+                          f"{r['sparse_gbs']:6.0f} GB/s | dense {r['dense_us']:8.1f} us | x{r['speedup']:.2f} "
+                          f"gate={'sparse' if r['gate_picks_sparse'] else 'dense'} err {err:.1e}", flush=True)
+                del ws, wd
+    else:
+        H = args.hidden or 4096
+        I = args.inter or 14336
+        dt = torch.bfloat16
+        mods = []
+        for c in range(2):           # two weight sets rotate through L2
+            lin = []
+            for seed, (o_f, i_f) in zip((1, 2, 3), ((I, H), (I, H), (H, I))):
+                g = torch.Generator(device=dev).manual_seed(seed + 10 * c)
+                w = (torch.randn(o_f, i_f, device=dev, generator=g) * 0.02).to(dt)
+                l = nn.Linear(i_f, o_f, bias=False, device=dev, dtype=dt)
+                l.weight.data = ops.prune_compress_24(w, want_values=False, want_meta=False, want_pruned=True)["pruned"]
+                lin.append(l)
+            mods.append(dict(lin=lin, sparse=SparseFlowFusedMLP(*lin, force_mode="sparse"),
+                             auto=SparseFlowFusedMLP(*lin, force_mode="auto")))
+        for M in [1, 8, 32, 128, 512, 2048, 8192]:
+            gx = torch.Generator(device=dev).manual_seed(1234)
+            x = torch.randn(M, H, device=dev, generator=gx).to(dt)
+            i = [0]
+
+            def dense():
+                g_, u_, d_ = mods[i[0] % 2]["lin"]
+                i[0] += 1
+                return d_(F.silu(g_(x)) * u_(x))
+
+            def arm(name):
+                def f():
+                    m = mods[i[0] % 2][name]
+                    i[0] += 1
+                    return m(x)
+                return f
+            with torch.no_grad():
+                td, ts, ta = timeit(dense, M), timeit(arm("sparse"), M), timeit(arm("auto"), M)
+            flops = 6.0 * M * H * I
+            r = dict(M=M, dense_us=td * 1e3, sparse_us=ts * 1e3, auto_us=ta * 1e3, auto_tflops=flops / ta / 1e9,
+                     sparse_tflops=flops / ts / 1e9, sparse_weight_gbs=3 * H * I * 1.125 / ts / 1e6,
+                     speedup_sparse=td / ts, speedup_auto=td / ta,
+                     gate_gate_up="sparse" if dispatch.should_use_sparse(M, H, 2 * I) else "dense",
+                     gate_down="sparse" if dispatch.should_use_sparse(M, I, H) else "dense")
+            rows.append(r)
+            print(f"M={M:5d}: dense {r['dense_us']:8.1f} us | sparse {r['sparse_us']:8.1f} us x{r['speedup_sparse']:.2f} "
+                  f"({r['sparse_tflops']:.0f} TF, weights {r['sparse_weight_gbs']:.0f} GB/s) | gated {r['auto_us']:8.1f} us "
+                  f"x{r['speedup_auto']:.2f} (gate|up {r['gate_gate_up']}, down {r['gate_down']})", flush=True)
+    ops.device_status()
+    if args.json:
+        with open(args.json, "w") as f:
+            json.dump({"gpu": torch.cuda.get_device_name(0), "sweep": args.sweep, "rows": rows}, f, indent=1)
+
+
+# ------------------------------------------------------------------------------------------------
 def main():
     args = parse_args()
     # Libraries (NCCL's version banner, for one) print to file descriptor 1.  Point fd 1 at stderr for
     # the rest of the run and keep the original for the JSON line, so stdout carries exactly one line.
     global _REAL_STDOUT
     sys.stdout.flush()
+    if args.only or args.sweep:
+        if args.only:
+            run_only(args)
+        else:
+            run_sweep(args)
+        return
     _REAL_STDOUT = os.dup(1)
     os.dup2(2, 1)
     if args.impl == "reference":
         run_reference_arm(args)
         return
 
-    import numpy as np
     import torch
     import torch.distributed as dist
     from sparseflow_b200 import _lib, ops, parallel
@@ -272,24 +503,19 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
-    H, I, M = WORKLOADS[args.workload]
-    if args.tokens:
-        M = args.tokens
+    H, I, M = workload_dims(args)
     dt = torch.bfloat16
+    sampler = ClockSampler(local_rank)
+    sampler.start()
 
     # ---- synthetic, seeded inputs (generated on the CPU so every rank and the oracle see the same bits)
-    def seeded(shape, seed, sigma):
-        g = torch.Generator().manual_seed(seed)
-        return (torch.randn(shape, generator=g, dtype=torch.float32) * sigma).to(dt)
-
-    wg = seeded((I, H), 1, 0.02).to(dev)
-    wu = seeded((I, H), 2, 0.02).to(dev)
-    wd = seeded((H, I), 3, 0.02).to(dev)
-    x_host = seeded((M, H), 1234, 1.0).pin_memory()
+    wg = seeded_cpu((I, H), 1, 0.02).to(dev)
+    wu = seeded_cpu((I, H), 2, 0.02).to(dev)
+    wd = seeded_cpu((H, I), 3, 0.02).to(dev)
+    x_host = seeded_cpu((M, H), 1234, 1.0).pin_memory()
     x = x_host.to(dev)
 
     # ---- weights: prune + compress once (load time), timed separately
-    # (output buffers allocated once: the timed loop is 20 back-to-back launches through the C ABI)
     pv = torch.empty((H, I // 2), dtype=dt, device=dev)
     pm = torch.empty(_lib.lib().sfb200_meta_bytes(H, I), dtype=torch.uint8, device=dev)
     st0 = torch.cuda.current_stream().cuda_stream
@@ -308,20 +534,24 @@ def main():
     prune_ms = t0.elapsed_time(t1) / 20
     del pv, pm
     prune_gbs = H * I * 3.125 / (prune_ms * 1e-3) / 1e9
+    prune_launches = 25
 
-    tp_mode = "single GPU"
+    exchange = "none (single GPU)"
     ffn = None
-    if world > 1 and args.tp == "fused":
+    if world > 1 and args.tp in ("fused", "scatter"):
         try:
-            ffn = parallel.FusedTensorParallelFFN(wg, wu, wd, max_tokens=M, use_switch_stores=args.tp_switch)
-            tp_mode = "fused: reduce-scatter in the down-GEMM epilogue (TMA stores to peer memory), all-gather in the reduction kernel"
+            ffn = parallel.FusedTensorParallelFFN(wg, wu, wd, max_tokens=M,
+                                                  exchange="auto" if args.tp == "fused" else "scatter")
+            exchange = ("one kernel per rank: barrier, in-switch reduction (multimem.ld_reduce), multimem.st of the finished block, barrier"
+                        if ffn.exchange == "switch" else
+                        "reduce-scatter in the down-GEMM epilogue (TMA stores to peer memory), all-gather in the reduction kernel")
         except Exception as exc:      # symmetric memory unavailable on this box: NCCL path
             sys.stderr.write(f"fused tensor-parallel path unavailable ({exc!r}); using NCCL all-reduce\n")
             ffn = None
     if ffn is None:
         ffn = parallel.TensorParallelFFN(wg, wu, wd, chunks=args.chunks)
         if world > 1:
-            tp_mode = f"NCCL all-reduce after the down GEMM, {args.chunks} chunk(s)"
+            exchange = f"NCCL all-reduce after the down GEMM, {args.chunks} chunk(s)"
     fused_tp = isinstance(ffn, parallel.FusedTensorParallelFFN)
     del wg, wu
     hidden = torch.empty((M, ffn.Ip), dtype=dt, device=dev)
@@ -337,49 +567,65 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def forced_gemms():
+        """The two GEMMs of the step, each with its own variant override when one was asked for."""
+        ops.force_token_tile(args.tile)
+        ops.sparse_gemm_swiglu(x, ffn.gu, out=hidden)
+        if args.tile_down:
+            ops.force_token_tile(args.tile_down)
+        ops.sparse_gemm(hidden, ffn.dn, out=out)
+
+    single = world == 1 and args.chunks == 1
     # ---- warm-up
     for _ in range(max(3, args.warmup)):
-        run_step()
+        if single:
+            forced_gemms()
+        else:
+            run_step()
     barrier()
     ops.device_status()
 
-    timed_step = run_step
-
     # ---- timed region: K steps; per-step events also bracket the gate|up kernel for the roofline
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     launches0 = ffn.kernel_launches
     barrier()
     s0 = torch.cuda.Event(enable_timing=True); s1 = torch.cuda.Event(enable_timing=True)
+    region_t0 = time.perf_counter()
     s0.record()
-    host_t0 = time.perf_counter()
-    if world == 1 and args.chunks == 1:
+    if single:
         for k in range(args.steps):
             ev[k][0].record()
+            if args.tile_down:
+                ops.force_token_tile(args.tile)
             ops.sparse_gemm_swiglu(x, ffn.gu, out=hidden)
             ev[k][1].record()
+            if args.tile_down:
+                ops.force_token_tile(args.tile_down)
             ops.sparse_gemm(hidden, ffn.dn, out=out)
             ev[k][2].record()
             ffn.kernel_launches += 2
     else:
         for k in range(args.steps):
-            timed_step()
-    host_enqueue_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps
+            res = run_step()
+    host_enqueue_ms = (time.perf_counter() - region_t0) * 1e3 / args.steps
     s1.record()
     barrier()
-    clocks = sampler.stop()
+    region_t1 = time.perf_counter()
+    clocks = sampler.summary(region_t0, region_t1)
     launches = ffn.kernel_launches - launches0
+    result = out if not fused_tp else res
     if fused_tp and args.tp_phases:       # after the timed region: ten more steps with events between the phases
-        names = ["gate_up_gemm", "down_gemm_scatter", "barrier_1", "reduce_allgather", "barrier_2"]
-        acc = [0.0] * 5
+        names = (["gate_up_gemm", "down_gemm", "exchange"] if ffn.exchange == "switch" else
+                 ["gate_up_gemm", "down_gemm_scatter", "barrier_1", "reduce_allgather", "barrier_2"])
+        acc = [0.0] * len(names)
         for _ in range(10):
             evs = []
             ffn.forward(x, phase_events=evs)
             torch.cuda.synchronize()
-            for i in range(5):
+            for i in range(len(names)):
                 acc[i] += evs[i].elapsed_time(evs[i + 1]) / 10
         sys.stderr.write(f"rank {rank} phases (ms): " + ", ".join(f"{n} {t:.4f}" for n, t in zip(names, acc)) + "\n")
+        result = ffn.forward(x)
     ops.device_status()
     ms_total = s0.elapsed_time(s1)
     tmax = torch.tensor([ms_total], dtype=torch.float64, device=dev)
@@ -389,28 +635,44 @@ def main():
     flops = 6.0 * M * H * I
     value = flops / (ms_step * 1e-3) / 1e12
 
+    # ---- parity: the step's output against the CPU oracle (outside every timed region)
+    parity = None
+    if not args.no_parity:
+        rows = args.parity_tokens or (1024 if args.workload == "llama70b_ffn" else M)
+        rows = min(rows, M)
+        torch.cuda.synchronize()
+        if rank == 0:
+            parity = parity_object(result, x_host, H, I, rows)
+        barrier()
+
     # ---- roofline of the dominant kernel (gate|up GEMM with SiLU.mul epilogue)
-    burst, sustained, hbm, src = measured_peaks()
+    burst, sustained_peak, hbm, src = measured_peaks()
     roof = None
-    if world == 1 and args.chunks == 1:
+    if single:
         gu_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
         dn_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
         gu_flops = 2.0 * M * (2 * I) * H
         achieved = gu_flops / (gu_ms * 1e-3) / 1e12
         peak = 2.0 * burst          # 2:4-sparse rate = 2 x the measured dense bf16 burst figure
+        nsm = torch.cuda.get_device_properties(dev).multi_processor_count
+        plan = _lib.lib().sfb200_debug_plan_gemm
+        dn_achieved = 2.0 * M * H * I / (dn_ms * 1e-3) / 1e12
         roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-                "kernel": "sparse_gemm_pair_kernel<256,128,4,SwiGLU> (gate|up)",
+                "kernel": f"sparse_gemm_pair_kernel, SiLU.mul epilogue (gate|up), variant {args.tile or plan(M, 2 * I, H, 1, nsm)}",
                 "peak_source": f"2 x bf16_tflops ({src}); of {'measured' if src == 'measured' else 'fallback'}",
-                "frac_of_sustained": achieved / (2.0 * sustained),
+                "frac_of_sustained": achieved / (2.0 * sustained_peak),
                 "ms_per_launch": gu_ms,
                 "step_ms_p50_p95": _p50_p95([e[0].elapsed_time(e[2]) for e in ev]),
-                "down_kernel": {"ms_per_launch": dn_ms, "achieved": 2.0 * M * H * I / (dn_ms * 1e-3) / 1e12}}
+                "down_kernel": {"ms_per_launch": dn_ms, "achieved": dn_achieved, "frac": dn_achieved / peak,
+                                "variant": args.tile_down or args.tile or plan(M, H, I, 0, nsm)},
+                "ffn_frac": value / peak}
 
-    # ---- end to end through the host-buffer C-ABI call (H2D of x, FFN, D2H of out, every step)
+    # ---- end to end with host buffers (H2D of x, FFN, D2H of out, every step)
     e2e = None
     if world == 1:
         L = _lib.lib()
+        ops.force_token_tile(0)
         W = _lib.FFNWeights(H, I, ops.BF16, ffn.gu.values.data_ptr(), ffn.gu.meta.data_ptr(),
                             ffn.dn.values.data_ptr(), ffn.dn.meta.data_ptr(), None)
         out_host = torch.empty((M, H), dtype=dt).pin_memory()
@@ -424,19 +686,60 @@ def main():
             L.sfb200_ffn_forward_host(C.byref(W), x_host.data_ptr(), out_host.data_ptr(), M, st)
         e1.record(); torch.cuda.synchronize()
         e2e_ms = e0.elapsed_time(e1) / args.steps
-        launches += 2 * args.steps
-        assert torch.equal(out_host.to(dev), out), "host-buffer path and device path disagree"
+        plan8 = (C.c_int * 8)()
+        launches += 2 * L.sfb200_debug_host_chunk_plan(M, 0, 0, plan8) * args.steps      # two kernels per token chunk
+        ops.sparse_gemm_swiglu(x, ffn.gu, out=hidden)
+        ops.sparse_gemm(hidden, ffn.dn, out=out)
+        chunked_equal = bool(torch.equal(out_host.to(dev), out))
         e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-               "h2d_bytes_per_step": M * H * 2, "d2h_bytes_per_step": M * H * 2, "ms_per_step": e2e_ms}
+               "h2d_bytes_per_step": M * H * 2, "d2h_bytes_per_step": M * H * 2, "ms_per_step": e2e_ms,
+               "call": "sfb200_ffn_forward_host (pinned host x -> chunked H2D / FFN / D2H pipeline -> pinned host out)",
+               "equals_device_path": chunked_equal}
+        if parity is not None:      # the host-buffer call's own output against the oracle, too
+            ph = parity_object(out_host.to(dev), x_host, H, I, parity["rows_checked"])
+            e2e["parity_chain"] = ph["chain"]
+            parity["ok"] = parity["ok"] and ph["ok"]
+    elif fused_tp and ffn.exchange == "switch":
+        # every rank uploads ONLY its own token rows, the rows are replicated through the switch, and every rank
+        # reads back ONLY the block it finished
+        lo, hi = ffn.owned_rows(M)
+        x_slice_host = x_host[lo:hi].clone().pin_memory()
+        x_slice = torch.empty((hi - lo, H), dtype=dt, device=dev)
+        out_host = torch.empty((hi - lo, H), dtype=dt).pin_memory()
+        for _ in range(2):
+            x_slice.copy_(x_slice_host, non_blocking=True)
+            r2 = ffn.forward_from_shards(x_slice, M)
+            out_host.copy_(r2[lo:hi], non_blocking=True)
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        l0 = ffn.kernel_launches
+        e0.record()
+        for _ in range(args.steps):
+            x_slice.copy_(x_slice_host, non_blocking=True)
+            r2 = ffn.forward_from_shards(x_slice, M)
+            out_host.copy_(r2[lo:hi], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        e1.record(); barrier()
+        launches += ffn.kernel_launches - l0
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item()) / args.steps
+        same = torch.tensor([int(torch.equal(out_host.to(dev), result[lo:hi]))], device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": M * H * 2, "d2h_bytes_per_step": M * H * 2, "ms_per_step": e2e_ms,
+               "call": "each rank: H2D of its own token rows, FusedTensorParallelFFN.forward_from_shards (all-gather through "
+                       "the switch + FFN + exchange), D2H of the block it finished; bytes are totals over ranks",
+               "equals_device_path": bool(same.item())}
     else:
-        # TP: every rank copies the replicated x in and rank 0 reads the result back
+        # NCCL / scatter path: every rank copies the replicated x in and rank 0 reads the result back
         out_host = torch.empty((M, H), dtype=dt).pin_memory()
         barrier()
         e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.steps):
             x.copy_(x_host, non_blocking=True)
-            res = timed_step()
+            res = run_step()
             if rank == 0:
                 out_host.copy_(res, non_blocking=True)
             torch.cuda.current_stream().synchronize()
@@ -445,13 +748,16 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item()) / args.steps
         e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-               "h2d_bytes_per_step": M * H * 2 * world, "d2h_bytes_per_step": M * H * 2, "ms_per_step": e2e_ms}
+               "h2d_bytes_per_step": M * H * 2 * world, "d2h_bytes_per_step": M * H * 2, "ms_per_step": e2e_ms,
+               "call": "every rank: H2D of the replicated x, forward; rank 0: D2H of the result"}
 
     # ---- dense cuBLAS on the same pruned weights, same shapes (library GEMM; the comparison line)
     dense = None
+    sustained = None
     if world == 1:
-        wgu_d = torch.cat([ops.decompress_24(ops.compress_weight(seeded((I, H), s, 0.02).to(dev))) for s in (1, 2)], 0)
+        wgu_d = torch.cat([ops.decompress_24(ops.compress_weight(seeded_cpu((I, H), s, 0.02).to(dev))) for s in (1, 2)], 0)
         wd_d = ops.decompress_24(ffn.dn)
+        gu_buf = torch.empty((M, 2 * I), dtype=dt, device=dev)
 
         def dense_step():
             gu = torch.matmul(x, wgu_d.t())
@@ -459,52 +765,94 @@ def main():
             h = torch.nn.functional.silu(g) * u
             return torch.matmul(h, wd_d.t())
 
+        def dense_gemms_only():
+            torch.matmul(x, wgu_d.t(), out=gu_buf)
+            torch.matmul(hidden, wd_d.t(), out=out)
+
         for _ in range(3):
             dense_step()
+            dense_gemms_only()
         torch.cuda.synchronize()
-        d0 = torch.cuda.Event(enable_timing=True); d1 = torch.cuda.Event(enable_timing=True); d2 = torch.cuda.Event(enable_timing=True)
-        d0.record()
+        d = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        d[0].record()
         for _ in range(args.steps):
             dense_step()
-        d1.record()
+        d[1].record()
         for _ in range(args.steps):
-            torch.matmul(x, wgu_d.t())
-        d2.record(); torch.cuda.synchronize()
-        dense_ms = d0.elapsed_time(d1) / args.steps
-        gemm_gu_ms = d1.elapsed_time(d2) / args.steps
+            torch.matmul(x, wgu_d.t(), out=gu_buf)
+        d[2].record()
+        for _ in range(args.steps):
+            torch.matmul(hidden, wd_d.t(), out=out)
+        d[3].record(); torch.cuda.synchronize()
+        dense_ms = d[0].elapsed_time(d[1]) / args.steps
+        gemm_gu_ms = d[1].elapsed_time(d[2]) / args.steps
+        gemm_dn_ms = d[2].elapsed_time(d[3]) / args.steps
         dense = {"ffn_ms": dense_ms, "ffn_tflops": flops / (dense_ms * 1e-3) / 1e12,
                  "speedup_ffn": dense_ms / ms_step,
                  "gate_up_gemm_ms": gemm_gu_ms, "gate_up_gemm_tflops": 2.0 * M * 2 * I * H / (gemm_gu_ms * 1e-3) / 1e12,
-                 "what": "torch.matmul (cuBLAS) on the same 2:4-pruned weights stored dense + torch silu*mul"}
-        del wgu_d, wd_d
+                 "down_gemm_ms": gemm_dn_ms, "down_gemm_tflops": 2.0 * M * I * H / (gemm_dn_ms * 1e-3) / 1e12,
+                 "speedup_gemm_only": (gemm_gu_ms + gemm_dn_ms) / ms_step,
+                 "what": "torch.matmul (cuBLAS) on the same 2:4-pruned weights stored dense; ffn_* adds torch silu*mul, "
+                         "speedup_gemm_only compares the two library GEMMs alone with the whole sparse step (which includes SiLU.mul)"}
+
+        # ---- sustained clocks: the same step looped for >= 2 s, then the two library GEMMs for >= 2 s
+        if not args.no_sustained:
+            sustained = {}
+            for name, fn, per_iter_ms in (("sparse_ffn", forced_gemms, ms_step), ("cublas_gemms_only", dense_gemms_only, gemm_gu_ms + gemm_dn_ms)):
+                iters = int(2200.0 / max(per_iter_ms, 0.05))
+                torch.cuda.synchronize()
+                a0 = torch.cuda.Event(enable_timing=True); a1 = torch.cuda.Event(enable_timing=True)
+                w0 = time.perf_counter()
+                a0.record()
+                for _ in range(iters):
+                    fn()
+                a1.record(); torch.cuda.synchronize()
+                w1 = time.perf_counter()
+                ms = a0.elapsed_time(a1) / iters
+                # skip the first 0.3 s of samples: clocks settle under the power cap
+                sustained[name] = {"ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12, "seconds": (w1 - w0),
+                                   "iterations": iters, "clocks": sampler.summary(w0 + 0.3, w1)}
+                if name == "sparse_ffn":
+                    launches += 2 * iters
+            sustained["speedup_gemm_only"] = sustained["cublas_gemms_only"]["ms_per_step"] / sustained["sparse_ffn"]["ms_per_step"]
+            sustained["frac_of_2x_sustained_peak"] = sustained["sparse_ffn"]["tflops"] / (2.0 * sustained_peak)
+        del wgu_d, wd_d, gu_buf
+    sampler.stop()
 
     # ---- CPU baseline (rank 0, N = 1): the oracle's FFN on a bounded token sample
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
-        toks = args.cpu_tokens or pick_cpu_tokens(H, I, threads)
-        t = cpu_reference_ffn(H, I, toks, threads, reps=2)
-        cpu = {"value": 6.0 * toks * H * I / t / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-               "sample": f"{toks} of {M} tokens, fp32 matmul on oracle-pruned weights, torch CPU, best of 2"}
+        torch.set_num_threads(threads)
+        toks = min(M, 1024)
+        xs = x_host[:toks]
+        oracle_ffn(xs, H, I)
+        best = float("inf")
+        for _ in range(3):
+            c0 = time.perf_counter()
+            oracle_ffn(xs, H, I).bfloat16()
+            best = min(best, time.perf_counter() - c0)
+        cpu = {"value": 6.0 * toks * H * I / best / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+               "sample": f"{toks} of {M} tokens, fp32 matmul on oracle-pruned weights, torch CPU, best of 3"}
 
     if rank == 0:
         line = {
             "metric": "dense_equiv_tflops_gated_ffn", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic",
-            "config": {"workload": f"{args.workload}: hidden {H}, intermediate {I}, {M} tokens, bf16, 2:4-pruned gate/up/down",
-                       "hidden": H, "intermediate": I, "tokens": M,
-                       "parallelism": "single GPU" if world == 1 else f"tp{world}: column-parallel gate/up, row-parallel down; {tp_mode}",
-                       "l2": "no flush: per-step working set (weights 152 MB + activations 157 MB for the default workload) exceeds the 126 MB L2"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "host_enqueue_ms_per_step": host_enqueue_ms,
-            "roofline": roof, "cpu_baseline": cpu, "dense_cublas": dense,
+            "data": "synthetic", "config": config_dict(args, H, I, M), "exchange": exchange,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches + prune_launches,
+            "host_enqueue_ms_per_step": host_enqueue_ms, "parity": parity,
+            "roofline": roof, "cpu_baseline": cpu, "dense_cublas": dense, "sustained": sustained,
             "prune_compress": {"ms": prune_ms, "gbs": prune_gbs, "frac_of_hbm": prune_gbs / hbm,
                                "what": f"down weight {H}x{I}, 3.125 B/element algorithmic"},
         }
         emit(line)
     if world > 1:
         dist.destroy_process_group()
+    if parity is not None and not parity["ok"]:
+        sys.stderr.write(f"PARITY FAILED: {parity}\n")
+        sys.exit(3)
 
 
 if __name__ == "__main__":

@@ -54,8 +54,20 @@ SFB200_API size_t sfb200_meta_bytes(int rows, int K);
 
 /* Synchronise the current device and return the device status word (0 = ok) of the kernels
  * launched so far; the word is cleared.  Non-zero: (code << 8) | detail, code 1 = a bounded
- * mbarrier wait ran out. */
+ * mbarrier wait ran out (detail = which wait: 1 operand slot free, 2 operands landed, 3 accumulator
+ * free, 4 accumulator complete).  Returns SFB200_ERROR_DEVICE when the word was non-zero.  Includes
+ * the word of sfb200_ffn_forward_noalloc (see sfb200_noalloc_device_status).  May allocate the
+ * per-device state on first use.  Plays the role of upstream's failure report that feeds the
+ * quarantine (runtime/dispatch/eligibility_policy.cpp:72-84): callers pass a non-zero result on
+ * to sf_record_sparse_failure. */
 SFB200_API int sfb200_device_status(int* status_word);
+
+/* Test hook for that failure path (no counterpart upstream): launches one small CTA that waits, with
+ * a limit of `limit_us` microseconds (1 .. 100000), on a barrier nothing arrives on.  The wait gives
+ * up, the kernel records (1 << 8) | where in the status word (the regular one, or the one of the
+ * allocation-free entry point when noalloc_word != 0) and returns by itself; nothing faults or traps
+ * and the context stays usable.  0 <= where <= 255. */
+SFB200_API int sfb200_debug_wait_timeout(unsigned limit_us, int where, int noalloc_word, void* stream);
 
 /* ------------------------------------------------------------------ 1. hot path ----------- */
 
@@ -174,6 +186,30 @@ SFB200_API int sfb200_reduce_allgather_switch(const void* slots, int tp, int row
                                               int dtype, const void* bias, void* stream);
 
 /*
+ * The exchange step in ONE launch per rank, through NVSwitch (no counterpart in the reference).  Every rank has
+ * written its partial output into its own copy of a symmetric buffer that also has a switch-replicated
+ * ("multicast") mapping.  The kernel waits until all ranks have (flag words in symmetric memory, bounded polls),
+ * sums this rank's token block across ranks inside the switch (multimem.ld_reduce, fp32 accumulation), adds the
+ * bias, rounds once, writes the finished block into every rank's output (multimem.st), and returns once every
+ * rank has finished, so the caller's next kernel may overwrite the partial buffer.
+ *   mc_partial_block  this rank's token block ([rows, cols]) inside the MULTICAST mapping of the partial buffer
+ *   mc_out_block      the same block inside the multicast mapping of the output tensor
+ *   peer_flags        HOST array of tp device pointers: every rank's flag array (sfb200_tp_flag_words() uint32,
+ *                     zero before the first launch, symmetric memory, used by no one else)
+ *   epoch             1, 2, 3, ...: one per launch on these flags, the same on every rank
+ * Every rank must make the same sequence of calls.  A peer that never arrives makes the wait give up after 2 s:
+ * sfb200_device_status then reports (2 << 8) | phase and the output is not valid.
+ */
+SFB200_API int sfb200_tp_allreduce_switch(const void* mc_partial_block, void* mc_out_block, int rows, int cols,
+                                          int dtype, const void* bias, void* const* peer_flags, int tp, int rank,
+                                          unsigned epoch, void* stream);
+/* Same protocol, no reduction: local_block ([rows, cols] 16-bit, LOCAL memory) is copied into mc_dst_block on every
+ * rank (an all-gather of one block per rank, e.g. of the activations each rank uploaded). */
+SFB200_API int sfb200_tp_allgather_switch(const void* local_block, void* mc_dst_block, int rows, int cols,
+                                          void* const* peer_flags, int tp, int rank, unsigned epoch, void* stream);
+SFB200_API int sfb200_tp_flag_words(void);
+
+/*
  * Gated FFN forward for callers that cannot allocate device memory (no counterpart in the
  * reference).  Same computation and bits as sfb200_ffn_forward, but the M x I hidden tensor lives
  * in a fixed array inside the library image, so this call and everything under it performs no
@@ -184,11 +220,19 @@ SFB200_API int sfb200_reduce_allgather_switch(const void* slots, int tp, int row
  *   - every GPU that loads the library holds the array until the process exits;
  *   - all calls on a device share the array: calls that overlap on the GPU race, serialise them;
  *   - the first call on a device resolves the array's device address: issue it before any stream
- *     capture begins.
+ *     capture begins;
+ *   - "allocates nothing" covers this library's own calls; the CUDA runtime may still load a kernel's
+ *     module at that kernel's first launch on a device (one more reason to call once at start-up).
  */
 #define SFB200_NOALLOC_SCRATCH_BYTES (16u << 20)
 SFB200_API int sfb200_ffn_forward_noalloc(const sfb200_ffn_weights* w, const void* x, int ldx, void* out,
                                           int ldo, int M, void* stream);
+/* Status word of sfb200_ffn_forward_noalloc on the current device (no counterpart upstream): the
+ * word lives in the library image like the scratch, so reading it allocates nothing either.
+ * Synchronises the device, returns the word in *status_word (may be NULL) and clears it;
+ * SFB200_ERROR_DEVICE when it was non-zero (a bounded wait inside that entry point's kernels ran
+ * out: the output of that call is not valid).  0 when the entry point never ran on this device. */
+SFB200_API int sfb200_noalloc_device_status(int* status_word);
 
 /*
  * Persistent form of one compressed weight (host-only helpers, no GPU work): a 256-byte header
@@ -221,7 +265,8 @@ SFB200_API int sfb200_blob_read_header(const void* header_host, size_t available
 
 /* Tuning hook: force the kernel variant / token tile on the current device.  0 = automatic;
  * 8 = decode kernel (M <= 32); 32/64/128/192/256 = single-CTA kernel with that token tile; 1256 =
- * CTA-pair kernel, 256-row x 256-token tiles; 2192/2208/2224/2240 = CTA-pair kernel, 512-row tiles
+ * CTA-pair kernel, 256-row x 256-token tiles; 1192/1208/1224/1240 = the same with that many tokens and
+ * two accumulator sets; 2192/2208/2224/2240 = CTA-pair kernel, 512-row tiles
  * with that many tokens; 3032/3064/3128 and 4032/4064/4128 = split-K cluster kernel with 2 or 4
  * K slices and a 32/64/128-token tile.  No counterpart upstream. */
 SFB200_API int sfb200_debug_force_token_tile(int bn);
@@ -261,13 +306,52 @@ SFB200_API int32_t sf_select_kernel(const char* cache_path, const sf_matmul_desc
 SFB200_API int32_t sf_cache_size(const char* cache_path);
 SFB200_API void sf_cache_clear(const char* cache_path);
 
+/*
+ * C form of the dispatcher call that upstream only offers in C++,
+ * KernelDispatcher::select_kernel(desc, gpu, A, B, C, stream)
+ * (runtime/dispatch/kernel_dispatcher.cpp:42-188): d_weight = the DEVICE weight matrix [desc.M, desc.K]
+ * (the 2:4 operand), d_x = activations [desc.N, desc.K], d_y = output [desc.N, desc.M]; any may be NULL.
+ * With a weight, the "compression cached" eligibility rule is evaluated on its content (FNV-1a of the
+ * first KiB + shape: runtime/cache/compressed_cache.cpp:9-29, kernel_dispatcher.cpp:67-80); when all
+ * three are given, sparse and dense candidates are timed on them (and d_y is overwritten), otherwise on
+ * synthetic buffers.  sf_select_kernel is this call with NULL matrices, as upstream
+ * (api/sparseflow_api.cpp:44) -- through it alone a 2:4 shape is never eligible, upstream and here.
+ */
+SFB200_API int32_t sf_select_kernel_ex(const char* cache_path, const sf_matmul_desc* desc,
+                                       const sf_gpu_info* gpu, const void* d_weight, const void* d_x,
+                                       void* d_y);
+/*
+ * Content-keyed store of compressed weights (runtime/cache/compressed_cache.cpp:31-104; upstream fills
+ * it inside its sparse launcher, kernels/sparse_cusparselt_24.cu:70-89).  Prunes + compresses the
+ * DEVICE weight [desc.M, desc.K] into library-owned device buffers (layout of sfb200_sparse_gemm),
+ * remembers them under (content hash, M, N, K, dtype, sparsity, device) and returns 1; a second call
+ * with the same content returns the same buffers.  Returns 0 when the shape or dtype has no sparse
+ * kernel, on a CUDA failure, or when the store would exceed its 1 GiB cap
+ * (compressed_cache.cpp:42,70-74).  *values / *meta (may be NULL) receive the device pointers, owned by
+ * the library until sf_compressed_cache_clear.  Synchronous.
+ */
+SFB200_API int32_t sf_compress_weight(const sf_matmul_desc* desc, const void* d_weight,
+                                      const void** values, const void** meta);
+SFB200_API int32_t sf_compressed_cache_count(void);  /* compressed_cache.cpp:94-97 */
+SFB200_API uint64_t sf_compressed_cache_bytes(void); /* compressed_cache.cpp:89-92 */
+SFB200_API void sf_compressed_cache_clear(void);     /* compressed_cache.cpp:83-87; frees the buffers */
+
 /* Additions behind the same cache (no counterpart upstream; they make the dispatcher's
  * "compression cached" rule and failure quarantine reachable through the C ABI, which upstream
- * only reaches from C++: runtime/dispatch/kernel_dispatcher.cpp:67-98,165-174). */
+ * only reaches from C++: runtime/dispatch/kernel_dispatcher.cpp:67-98,165-174).
+ * sf_note_compressed declares a shape's weight compressed without handing the matrix over. */
 SFB200_API void sf_note_compressed(const char* cache_path, const sf_matmul_desc* desc);
 SFB200_API void sf_record_sparse_failure(const char* cache_path, const sf_matmul_desc* desc,
                                          const sf_gpu_info* gpu);
 SFB200_API int32_t sf_bucket_dimension(int32_t dim); /* kernel_dispatcher.cpp:16-28 */
+/* Decision counters of the selector behind cache_path (upstream only prints "[Cache HIT]" etc. to
+ * stdout, kernel_dispatcher.cpp:59,87,101): out[0..n) = calls, cache hits, misses, benchmark runs,
+ * dense decisions, sparse decisions, sparse failures recorded, SPARSEFLOW_FORCE bypasses.  Returns
+ * the number of counters written (at most 8). */
+SFB200_API int32_t sf_get_counters(const char* cache_path, int64_t* out, int32_t n);
+/* Environment: SPARSEFLOW_LOG=1 (decisions to stderr), SPARSEFLOW_CACHE_DB (database used for a NULL
+ * cache_path instead of "kernel_cache.db"), SPARSEFLOW_FORCE=dense|sparse (every call returns 0, or 2
+ * for shapes the sparse kernel supports, without lookup, measurement or persistence). */
 
 /* ------------------------------------------------------------------ 3. C ABI v1 ----------- */
 /* experiments/old_structure/include/sparseflow/c_api.h:38-200; src/runtime/context.cpp:78-300. */

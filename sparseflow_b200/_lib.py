@@ -75,7 +75,30 @@ def lib() -> C.CDLL:
     L.sfb200_sparse_gemm_scatter.argtypes = [vp, i, vp, vp, C.POINTER(vp), i, i, i, i, i, i, vp]
     L.sfb200_reduce_allgather.argtypes = [vp, i, i, i, C.POINTER(vp), i, vp, vp]
     L.sfb200_reduce_allgather_switch.argtypes = [vp, i, i, i, vp, i, vp, vp]
+    L.sfb200_tp_allreduce_switch.argtypes = [vp, vp, i, i, i, vp, C.POINTER(vp), i, i, C.c_uint, vp]
+    L.sfb200_tp_allgather_switch.argtypes = [vp, vp, i, i, C.POINTER(vp), i, i, C.c_uint, vp]
     L.sfb200_ffn_forward_noalloc.argtypes = [C.POINTER(FFNWeights), vp, i, vp, i, i, vp]
+    L.sfb200_noalloc_device_status.argtypes = [C.POINTER(C.c_int)]
+    L.sfb200_debug_wait_timeout.argtypes = [C.c_uint, i, i, vp]
+    L.sf_select_kernel.restype = C.c_int32
+    L.sf_select_kernel.argtypes = [C.c_char_p, C.POINTER(MatmulDesc), C.POINTER(GpuInfo)]
+    L.sf_select_kernel_ex.restype = C.c_int32
+    L.sf_select_kernel_ex.argtypes = [C.c_char_p, C.POINTER(MatmulDesc), C.POINTER(GpuInfo), vp, vp, vp]
+    L.sf_cache_size.restype = C.c_int32
+    L.sf_cache_size.argtypes = [C.c_char_p]
+    L.sf_cache_clear.restype = None
+    L.sf_cache_clear.argtypes = [C.c_char_p]
+    L.sf_note_compressed.restype = None
+    L.sf_note_compressed.argtypes = [C.c_char_p, C.POINTER(MatmulDesc)]
+    L.sf_record_sparse_failure.restype = None
+    L.sf_record_sparse_failure.argtypes = [C.c_char_p, C.POINTER(MatmulDesc), C.POINTER(GpuInfo)]
+    L.sf_compress_weight.restype = C.c_int32
+    L.sf_compress_weight.argtypes = [C.POINTER(MatmulDesc), vp, C.POINTER(vp), C.POINTER(vp)]
+    L.sf_compressed_cache_count.restype = C.c_int32
+    L.sf_compressed_cache_bytes.restype = C.c_uint64
+    L.sf_compressed_cache_clear.restype = None
+    L.sf_get_counters.restype = C.c_int32
+    L.sf_get_counters.argtypes = [C.c_char_p, C.POINTER(C.c_int64), C.c_int32]
     L.sfb200_debug_force_token_tile.argtypes = [i]
     L.sfb200_debug_plan_gemm.argtypes = [i, i, i, i, i]
     L.sfb200_debug_host_pipeline.argtypes = [i, i]

@@ -4,11 +4,22 @@
 
 #include <mutex>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "../../include/sparseflow_b200.h"
 #include "device_state.h"
 #include "kernels.h"
 
 using namespace sfb200;
+
+namespace {
+// NVTX range around the host side of a launch sequence (prune, gate|up GEMM, down GEMM, exchange):
+// shows up in a timeline tool when one is attached, costs a pointer test otherwise.
+struct Range {
+  explicit Range(const char* name) { nvtxRangePushA(name); }
+  ~Range() { nvtxRangePop(); }
+};
+}  // namespace
 
 namespace sfb200 {
 
@@ -23,9 +34,9 @@ DeviceState* device_state(int* err) {
     return nullptr;
   }
   DeviceState* s = &g_states[dev];
-  if (s->ready) return s;
+  if (s->ready.load(std::memory_order_acquire)) return s;
   std::lock_guard<std::mutex> lk(g_state_mu);
-  if (s->ready) return s;
+  if (s->ready.load(std::memory_order_relaxed)) return s;
   cudaDeviceProp prop;
   if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) {
     if (err) *err = kErrCuda;
@@ -44,7 +55,7 @@ DeviceState* device_state(int* err) {
     cudaGetLastError();
     return nullptr;
   }
-  s->ready = true;
+  s->ready.store(true, std::memory_order_release);
   return s;
 }
 
@@ -106,6 +117,10 @@ int sfb200_device_status(int* status_word) {
   int w = 0;
   if (cudaMemcpy(&w, s->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return kErrCuda;
   if (w != 0) cudaMemset(s->status, 0, sizeof(int));
+  // the allocation-free FFN entry point keeps its own word (in the library image); fold it in
+  int wn = 0;
+  if (noalloc_take_status(&wn) != kOk) return kErrCuda;
+  if (w == 0) w = wn;
   if (status_word) *status_word = w;
   return w == 0 ? kOk : kErrDevice;
 }
@@ -114,6 +129,7 @@ int sfb200_prune_compress_24(const void* dense, int rows, int K, int ld, int dty
                              void* values, void* meta, void* ref_codes, void* pruned, void* stream) {
   int err = kOk;
   if (!device_state(&err)) return err;
+  Range r("sfb200.prune_compress");
   PruneArgs a{};
   a.dense = dense;
   a.rows = rows;
@@ -133,6 +149,7 @@ int sfb200_prune_compress_gate_up(const void* gate, const void* up, int I, int K
   int err = kOk;
   if (!device_state(&err)) return err;
   if (gate == nullptr || up == nullptr || I % 16 != 0) return kErrInvalid;
+  Range r("sfb200.prune_compress_gate_up");
   PruneArgs a{};
   a.dense = gate;
   a.dense2 = up;
@@ -197,6 +214,7 @@ int sfb200_sparse_gemm(const void* x, int ldx, const void* values, const void* m
   int err = kOk;
   DeviceState* s = device_state(&err);
   if (!s) return err;
+  Range r("sfb200.sparse_gemm");
   return run_gemm(s, x, ldx, values, meta, y, ldy, M, N, K, dtype, bias, act, kEpiStore, 0,
                   static_cast<cudaStream_t>(stream));
 }
@@ -206,6 +224,7 @@ int sfb200_sparse_gemm_swiglu(const void* x, int ldx, const void* values_gu, con
   int err = kOk;
   DeviceState* s = device_state(&err);
   if (!s) return err;
+  Range r("sfb200.gate_up_gemm");
   return run_gemm(s, x, ldx, values_gu, meta_gu, h, ldh, M, 2 * I, K, dtype, nullptr, kActNone,
                   kEpiSwiGLU, 0, static_cast<cudaStream_t>(stream));
 }
@@ -225,9 +244,14 @@ int sfb200_ffn_forward(const sfb200_ffn_weights* w, const void* x, int ldx, void
   if (!s) return err;
   if (!w || !hidden) return kErrInvalid;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int rc = run_gemm(s, x, ldx, w->gu_values, w->gu_meta, hidden, w->I, M, 2 * w->I, w->H, w->dtype,
-                    nullptr, kActNone, kEpiSwiGLU, 0, st);
+  int rc;
+  {
+    Range r("sfb200.gate_up_gemm");
+    rc = run_gemm(s, x, ldx, w->gu_values, w->gu_meta, hidden, w->I, M, 2 * w->I, w->H, w->dtype,
+                  nullptr, kActNone, kEpiSwiGLU, 0, st);
+  }
   if (rc != kOk) return rc;
+  Range r("sfb200.down_gemm");
   return run_gemm(s, hidden, w->I, w->down_values, w->down_meta, out, ldo, M, w->H, w->I, w->dtype,
                   w->down_bias, kActNone, kEpiStore, 0, st);
 }
@@ -340,6 +364,7 @@ int sfb200_sparse_gemm_scatter(const void* x, int ldx, const void* values, const
   a.epi = kEpiStore;
   a.act = kActNone;
   a.num_sms = s->num_sms;
+  Range r("sfb200.down_gemm_scatter");
   return launch_sparse_gemm_pair_scatter(a, peer_slots, tp, tok_per_owner, static_cast<cudaStream_t>(stream));
 }
 
@@ -348,6 +373,7 @@ int sfb200_reduce_allgather(const void* slots, int tp, int rows, int cols, void*
   int err = kOk;
   if (!device_state(&err)) return err;
   if (!peer_out_blocks) return kErrInvalid;
+  Range r("sfb200.reduce_allgather");
   return launch_reduce_allgather(slots, tp, rows, cols, peer_out_blocks, nullptr, dtype, bias,
                                  static_cast<cudaStream_t>(stream));
 }
@@ -360,6 +386,29 @@ int sfb200_reduce_allgather_switch(const void* slots, int tp, int rows, int cols
   return launch_reduce_allgather(slots, tp, rows, cols, nullptr, switch_out_block, dtype, bias,
                                  static_cast<cudaStream_t>(stream));
 }
+
+int sfb200_tp_allreduce_switch(const void* mc_partial_block, void* mc_out_block, int rows, int cols, int dtype,
+                               const void* bias, void* const* peer_flags, int tp, int rank, unsigned epoch,
+                               void* stream) {
+  int err = kOk;
+  DeviceState* s = device_state(&err);
+  if (!s) return err;
+  Range r("sfb200.tp_allreduce_switch");
+  return launch_switch_exchange(true, mc_partial_block, mc_out_block, rows, cols, dtype, bias, peer_flags, tp, rank,
+                                epoch, s->status, static_cast<cudaStream_t>(stream));
+}
+
+int sfb200_tp_allgather_switch(const void* local_block, void* mc_dst_block, int rows, int cols, void* const* peer_flags,
+                               int tp, int rank, unsigned epoch, void* stream) {
+  int err = kOk;
+  DeviceState* s = device_state(&err);
+  if (!s) return err;
+  Range r("sfb200.tp_allgather_switch");
+  return launch_switch_exchange(false, local_block, mc_dst_block, rows, cols, kBF16, nullptr, peer_flags, tp, rank,
+                                epoch, s->status, static_cast<cudaStream_t>(stream));
+}
+
+int sfb200_tp_flag_words(void) { return kSwitchFlagWords; }
 
 /* Test / tuning hook: force the token tile of the tcgen05 kernel (0 = automatic). */
 SFB200_API int sfb200_debug_force_token_tile(int bn) {

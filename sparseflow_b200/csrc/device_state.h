@@ -3,12 +3,14 @@
 #include <cuda_runtime.h>
 #include <stddef.h>
 
+#include <atomic>
+
 namespace sfb200 {
 
 constexpr int kMaxDevices = 16;
 
 struct DeviceState {
-  bool ready = false;
+  std::atomic<bool> ready{false};
   int cc = 0;
   int num_sms = 0;
   size_t total_mem = 0;
@@ -31,5 +33,10 @@ struct DeviceState {
 // State of the current device, created on first use.  Returns nullptr and sets *err when there is
 // no usable sm_100 device.
 DeviceState* device_state(int* err);
+
+// Status word of sfb200_ffn_forward_noalloc on the current device (it lives in the library image, not in
+// DeviceState): synchronises, reads and clears it; *word = 0 when that entry point never ran here.
+int noalloc_take_status(int* word);
+int* noalloc_status_word();   // its device address (sets the entry point up on the current device), or nullptr
 
 }  // namespace sfb200

@@ -17,10 +17,17 @@
 // element of the M x I region before the down kernel reads it.
 //
 // The first call on each device looks up the array's device address (and sets kernel attributes);
-// make that call before starting any stream capture.
+// make that call before starting any stream capture.  "Allocates nothing" is a statement about this
+// library's own calls: the CUDA runtime may still load a kernel's module the first time that kernel
+// is launched on a device, which is one more reason to make the first call during start-up.
+//
+// Device-side failures (a bounded wait that ran out) of this entry point are recorded in a status
+// word that is also part of the library image; sfb200_noalloc_device_status reads and clears it
+// without allocating, and sfb200_device_status includes it.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "../../include/sparseflow_b200.h"
@@ -38,7 +45,7 @@ static __device__ __align__(256) unsigned char g_hidden_scratch[kScratchBytes];
 static __device__ __align__(256) int g_status_word[64];
 
 struct NoAllocDevice {
-  bool ready = false;
+  std::atomic<bool> ready{false};
   void* scratch = nullptr;
   int* status = nullptr;
   int num_sms = 0;
@@ -54,9 +61,9 @@ int setup_current_device(NoAllocDevice** out) {
     return kErrCuda;
   }
   NoAllocDevice* d = &g_dev[dev];
-  if (!d->ready) {
+  if (!d->ready.load(std::memory_order_acquire)) {
     std::lock_guard<std::mutex> lk(g_mu);
-    if (!d->ready) {
+    if (!d->ready.load(std::memory_order_relaxed)) {
       int major = 0, sms = 0;
       if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
           cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
@@ -74,7 +81,7 @@ int setup_current_device(NoAllocDevice** out) {
       d->scratch = sp;
       d->status = static_cast<int*>(st);
       d->num_sms = sms;
-      d->ready = true;
+      d->ready.store(true, std::memory_order_release);
     }
   }
   *out = d;
@@ -82,9 +89,44 @@ int setup_current_device(NoAllocDevice** out) {
 }
 
 }  // namespace
+
+// Device address of that status word on the current device (performs the per-device set-up if needed);
+// nullptr when the device is unusable.  Used by the bounded-wait probe to exercise this word's read path.
+int* noalloc_status_word() {
+  NoAllocDevice* d = nullptr;
+  return setup_current_device(&d) == kOk ? d->status : nullptr;
+}
+
+// Status word of the allocation-free entry point on the current device: synchronises, reads and
+// clears it.  *word = 0 and kOk when that entry point has not run on this device.
+int noalloc_take_status(int* word) {
+  *word = 0;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    cudaGetLastError();
+    return kErrCuda;
+  }
+  NoAllocDevice* d = &g_dev[dev];
+  if (!d->ready.load(std::memory_order_acquire)) return kOk;
+  if (cudaDeviceSynchronize() != cudaSuccess) return kErrCuda;
+  int w = 0;
+  if (cudaMemcpy(&w, d->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return kErrCuda;
+  if (w != 0 && cudaMemset(d->status, 0, sizeof(int)) != cudaSuccess) return kErrCuda;
+  *word = w;
+  return kOk;
+}
+
 }  // namespace sfb200
 
 using namespace sfb200;
+
+extern "C" int sfb200_noalloc_device_status(int* status_word) {
+  int w = 0;
+  const int rc = noalloc_take_status(&w);
+  if (status_word) *status_word = w;
+  if (rc != kOk) return rc;
+  return w == 0 ? kOk : kErrDevice;
+}
 
 extern "C" int sfb200_ffn_forward_noalloc(const sfb200_ffn_weights* w, const void* x, int ldx, void* out,
                                           int ldo, int M, void* stream) {

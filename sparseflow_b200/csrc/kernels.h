@@ -67,13 +67,13 @@ struct SparseGemmArgs {
 };
 int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream);
 // CTA-pair (cta_group::2) variant, 256-row x 256-token tiles; chosen by launch_sparse_gemm for
-// m_tok >= kPairMinTokens.  force_bn 1256 (256-row tiles) or 2192..2240 (512-row tiles) picks a variant.
+// m_tok >= kPairMinTokens.  force_bn 1192..1256 (256-row tiles) or 2192..2240 (512-row tiles) picks a variant.
 int launch_sparse_gemm_pair(const SparseGemmArgs& a, cudaStream_t stream);
 constexpr int kPairMinTokens = 1024;
-// Variant the CTA-pair launcher picks on its own (1256 or 2192..2240).
+// Variant the CTA-pair launcher picks on its own (1192..1256 or 2192..2240).
 int pick_pair_variant(int n_out, int m_tok, int K, int num_sms);
 // The kernel variant launch_sparse_gemm runs for a shape when nothing is forced, in the numbering of
-// SparseGemmArgs::force_bn: 8 decode kernel; 32..256 single-CTA kernel with that token tile; 1256 / 2192..2240
+// SparseGemmArgs::force_bn: 8 decode kernel; 32..256 single-CTA kernel with that token tile; 1192..1256 / 2192..2240
 // CTA-pair kernel; 3000 + tile / 4000 + tile split-K cluster kernel with 2 / 4 K slices.  Host-only.
 int plan_sparse_gemm(int m_tok, int n_out, int K, int epi, int num_sms);
 // Row-parallel GEMM of a tensor-parallel FFN with the reduce-scatter fused into the epilogue:
@@ -87,6 +87,18 @@ int launch_sparse_gemm_pair_scatter(const SparseGemmArgs& a, void* const* peer_s
 // store reaches every rank) and peer_out_blocks is ignored.
 int launch_reduce_allgather(const void* slots, int tp, int rows, int cols, void* const* peer_out_blocks,
                             void* switch_out_block, int fmt, const void* bias, cudaStream_t stream);
+
+// The exchange step in one launch, through the switch-replicated (multicast) mappings of symmetric buffers.
+// reduce = true:  src = this rank's token block inside the MULTICAST mapping of the partial-sum buffer; the block is
+//                 summed across ranks in the switch (fp32 accumulation), bias added, rounded once and written to
+//                 mc_dst, this rank's block inside the multicast mapping of the output (every rank receives it).
+// reduce = false: src = LOCAL data ([rows, cols]), copied to mc_dst on every rank (all-gather of one block per rank).
+// peer_flags: HOST array of tp device pointers, every rank's flag array of kSwitchFlagWords uint32 (zeroed once,
+// symmetric memory); epoch: 1, 2, 3, ... one per launch, the same on every rank.  Bounded waits; on a timeout the
+// status word receives (2 << 8) | phase.
+constexpr int kSwitchFlagWords = 2 * 148 * 8;
+int launch_switch_exchange(bool reduce, const void* src, void* mc_dst, int rows, int cols, int fmt, const void* bias,
+                           void* const* peer_flags, int tp, int rank, unsigned epoch, int* status, cudaStream_t stream);
 
 // Split-K variant of the single-CTA kernel: a cluster of `split` (2 or 4) CTAs shares one output tile,
 // each streaming a slice of K; partial tiles are reduced through distributed shared memory.  Chosen by

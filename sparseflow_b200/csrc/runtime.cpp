@@ -11,6 +11,21 @@
 //   cache/kernel_key.cpp:7-17            key string "M=..;N=..;K=..;dtype=..;layout=..;sp=..;sm=.."
 //   benchmark/micro_bench.cpp:37-49,71-174 L2 flush, 3 warm-up + 10 timed, CV > 5 % => one retry
 //
+//   cache/compressed_cache.cpp:9-104    content-keyed store of compressed weights (FNV-1a of the first
+//                                       KiB of the device matrix + shape), 1 GiB cap; consulted at
+//                                       dispatch/kernel_dispatcher.cpp:67-80
+//
+// Upstream's C entry point passes no matrix (api/sparseflow_api.cpp:44: A = B = C = nullptr), so through
+// sf_select_kernel alone its "compression cached" rule can never hold and every 2:4 shape is cached
+// as dense; the dispatcher's pointer-taking form is C++ only.  The same is true here for
+// sf_select_kernel; sf_select_kernel_ex is the C form of that C++ call (device pointers), and
+// sf_compress_weight fills the content-keyed store the way upstream's sparse launcher does
+// (kernels/sparse_cusparselt_24.cu:70-89).
+//
+// Environment: SPARSEFLOW_LOG=1 logs decisions to stderr; SPARSEFLOW_CACHE_DB replaces the default
+// database path used for a NULL cache_path; SPARSEFLOW_FORCE=dense|sparse bypasses lookup and
+// measurement and returns kernel 0 / 2 for every eligible-by-shape request (nothing is persisted).
+//
 // Differences, on purpose: the winner is the candidate with the lower measured time (the reference
 // halves the sparse flop count before comparing GFLOPS, which makes sparse need a 2x win); each
 // store is guarded by its own mutex; libsqlite3 and libcublas are resolved with dlopen at first use
@@ -30,6 +45,7 @@
 #include <mutex>
 #include <set>
 #include <string>
+#include <tuple>
 #include <vector>
 
 #include "../../include/sparseflow_b200.h"
@@ -332,32 +348,174 @@ struct Timing {
   double cv = 0;
 };
 
+// ---------------------------------------------------------------- compressed-weight store
+// Process-wide, keyed by content: FNV-1a 64 of the first KiB of the DEVICE matrix plus the shape, as
+// upstream (cache/compressed_cache.cpp:9-29, compressed_cache.h:10-21 -- whose key narrows M, N, K to
+// 16 bits; full ints here).  Values are library-owned device buffers in the layout the sparse GEMM
+// consumes; entries are never evicted, and a put that would exceed 1 GiB is refused
+// (compressed_cache.cpp:42,70-74).
+uint64_t device_matrix_hash(const void* d_data, size_t bytes) {
+  unsigned char sample[1024];
+  const size_t n = bytes < sizeof(sample) ? bytes : sizeof(sample);
+  if (n == 0 || cudaMemcpy(sample, d_data, n, cudaMemcpyDeviceToHost) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  uint64_t h = 14695981039346656037ull;
+  for (size_t i = 0; i < n; ++i) {
+    h ^= sample[i];
+    h *= 1099511628211ull;
+  }
+  return h;
+}
+
+struct CompressedKey {
+  uint64_t content_hash;
+  int32_t M, N, K, dtype, sparsity_type, device;
+  bool operator<(const CompressedKey& o) const {
+    return std::tie(content_hash, M, N, K, dtype, sparsity_type, device) <
+           std::tie(o.content_hash, o.M, o.N, o.K, o.dtype, o.sparsity_type, o.device);
+  }
+};
+struct CompressedValue {
+  void* values = nullptr;
+  void* meta = nullptr;
+  size_t bytes = 0;
+};
+class CompressedStore {
+ public:
+  static constexpr size_t kMaxBytes = 1ull << 30;
+  bool contains(const CompressedKey& k) {
+    std::lock_guard<std::mutex> lk(mu_);
+    return map_.count(k) != 0;
+  }
+  bool get(const CompressedKey& k, CompressedValue* out) {
+    std::lock_guard<std::mutex> lk(mu_);
+    auto it = map_.find(k);
+    if (it == map_.end()) return false;
+    *out = it->second;
+    return true;
+  }
+  // Takes ownership of v's buffers on success; on refusal (cap) the caller frees them.
+  bool put(const CompressedKey& k, const CompressedValue& v) {
+    std::lock_guard<std::mutex> lk(mu_);
+    if (map_.count(k)) return false;
+    if (total_ + v.bytes > kMaxBytes) return false;
+    map_[k] = v;
+    total_ += v.bytes;
+    return true;
+  }
+  void clear() {
+    std::lock_guard<std::mutex> lk(mu_);
+    for (auto& kv : map_) {
+      int prev = 0;
+      cudaGetDevice(&prev);
+      cudaSetDevice(kv.first.device);
+      cudaFree(kv.second.values);
+      cudaFree(kv.second.meta);
+      cudaSetDevice(prev);
+    }
+    map_.clear();
+    total_ = 0;
+  }
+  size_t count() {
+    std::lock_guard<std::mutex> lk(mu_);
+    return map_.size();
+  }
+  size_t bytes() {
+    std::lock_guard<std::mutex> lk(mu_);
+    return total_;
+  }
+ private:
+  std::mutex mu_;
+  std::map<CompressedKey, CompressedValue> map_;
+  size_t total_ = 0;
+};
+CompressedStore& compressed_store() {
+  static CompressedStore* s = new CompressedStore;   // never destroyed: device buffers outlive static teardown
+  return *s;
+}
+
+bool make_compressed_key(const sf_matmul_desc& d, const void* d_weight, CompressedKey* k) {
+  if (!d_weight || d.M <= 0 || d.K <= 0) return false;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  const size_t bytes = static_cast<size_t>(d.M) * d.K * (d.dtype == 2 ? 4 : 2);
+  const uint64_t h = device_matrix_hash(d_weight, bytes);
+  if (h == 0) return false;
+  *k = CompressedKey{h, d.M, d.N, d.K, d.dtype, d.sparsity_type, dev};
+  return true;
+}
+
+int force_mode() {   // 0 none, 1 dense, 2 sparse
+  const char* e = getenv("SPARSEFLOW_FORCE");
+  if (!e || !*e) return 0;
+  if (!strcmp(e, "dense") || !strcmp(e, "DENSE")) return 1;
+  if (!strcmp(e, "sparse") || !strcmp(e, "SPARSE")) return 2;
+  return 0;
+}
+
+// Decision counters of one selector (index = position in the array sf_get_counters fills).
+enum Counter { kCtrCalls = 0, kCtrHits, kCtrMisses, kCtrBenchmarks, kCtrDense, kCtrSparse, kCtrFailures, kCtrForced, kNumCounters };
+
 class Selector {
  public:
   explicit Selector(const std::string& path) : store_(path) {}
 
-  int select(const sf_matmul_desc& d, const sf_gpu_info& g) {
+  // a, x, y: optional DEVICE matrices (weight [M, K], activations [N, K], output [N, M]); with a weight
+  // the "compression cached" rule is evaluated on its content, and when all three are given the
+  // candidates are timed on them instead of synthetic buffers.
+  int select(const sf_matmul_desc& d, const sf_gpu_info& g, const void* a = nullptr, const void* x = nullptr,
+             void* y = nullptr) {
     std::lock_guard<std::mutex> lk(mu_);
+    ctr_[kCtrCalls]++;
     const std::string key = make_key(d, g.sm_arch);
+    if (const int f = force_mode()) {
+      ctr_[kCtrForced]++;
+      const bool shape_ok = d.sparsity_type == 1 && (d.dtype == 0 || d.dtype == 1) && d.K % 64 == 0 && d.M % 8 == 0;
+      const int k = (f == 2 && shape_ok) ? kSparsePrefill : kDenseTc;
+      SF_LOG("SPARSEFLOW_FORCE: %s -> %d", key.c_str(), k);
+      return k;
+    }
     Entry e;
-    if (store_.get(key, &e) && !(e.sparse_failed && e.kernel == 0 && e.gflops == 0 && false)) {
-      SF_LOG("cache hit %s -> %d (%.1f GFLOPS)", key.c_str(), e.kernel, e.gflops);
-      return e.kernel;
+    if (store_.get(key, &e)) {
+      if (e.failure_count > failures_[key]) failures_[key] = e.failure_count;
+      // A row written only by a failure report (no measurement yet) must not pin the shape to dense:
+      // below the quarantine threshold it is measured like a miss.
+      const bool failure_stub = e.sparse_failed && e.kernel == kDenseTc && e.gflops == 0 && failures_[key] < kMaxFailures;
+      if (!failure_stub) {
+        ctr_[kCtrHits]++;
+        SF_LOG("cache hit %s -> %d (%.1f GFLOPS)", key.c_str(), e.kernel, e.gflops);
+        return e.kernel;
+      }
+    }
+    ctr_[kCtrMisses]++;
+    bool compression_cached = compressed_.count(compressed_key(d)) != 0;
+    CompressedValue cv;
+    if (a && d.sparsity_type == 1) {
+      CompressedKey ck;
+      if (make_compressed_key(d, a, &ck) && compressed_store().get(ck, &cv)) compression_cached = true;
     }
     std::string why;
-    if (!eligible(d, key, &why)) {
+    if (!eligible(d, key, compression_cached, &why)) {
       SF_LOG("sparse skipped for %s: %s; using dense", key.c_str(), why.c_str());
       store_.put_best(key, kDenseTc, 0.0);
+      ctr_[kCtrDense]++;
       return kDenseTc;
     }
     double dense_ms = -1, sparse_ms = -1;
-    const bool ran = benchmark(d, &dense_ms, &sparse_ms);
+    ctr_[kCtrBenchmarks]++;
+    const bool ran = benchmark(d, a, x, y, cv, &dense_ms, &sparse_ms);
     if (!ran) {
       SF_LOG("no device to benchmark on: dense, not cached");
       return kDenseTc;
     }
     if (sparse_ms <= 0) {
       failures_[key]++;
+      ctr_[kCtrFailures]++;
       store_.mark_failed(key, -1);
     }
     int best = kDenseTc;
@@ -369,6 +527,7 @@ class Selector {
     const double gflops = best_ms > 0 ? 2.0 * d.M * d.N * d.K / (best_ms * 1e6) : 0.0;
     SF_LOG("selected %d for %s: dense %.4f ms, sparse %.4f ms", best, key.c_str(), dense_ms, sparse_ms);
     store_.put_best(key, best, gflops);
+    ctr_[best == kDenseTc ? kCtrDense : kCtrSparse]++;
     return best;
   }
 
@@ -380,11 +539,22 @@ class Selector {
     std::lock_guard<std::mutex> lk(mu_);
     const std::string key = make_key(d, g.sm_arch);
     failures_[key]++;
+    ctr_[kCtrFailures]++;
     store_.mark_failed(key, -1);
+  }
+  int size() { return store_.size(); }
+  void clear() {
+    std::lock_guard<std::mutex> lk(mu_);
+    store_.clear();
+    failures_.clear();
+  }
+  void counters(int64_t* out) {
+    std::lock_guard<std::mutex> lk(mu_);
+    for (int i = 0; i < kNumCounters; ++i) out[i] = ctr_[i];
   }
 
  private:
-  bool eligible(const sf_matmul_desc& d, const std::string& key, std::string* why) {
+  bool eligible(const sf_matmul_desc& d, const std::string& key, bool compression_cached, std::string* why) {
     if (d.sparsity_type != 1) { *why = "Only 2:4 sparsity supported"; return false; }
     if (2.0 * d.M * d.N * d.K < kMinSparseFlops) { *why = "Matrix too small"; return false; }
     auto it = failures_.find(key);
@@ -392,7 +562,7 @@ class Selector {
       *why = "Sparse failed too many times for this shape";
       return false;
     }
-    if (!compressed_.count(compressed_key(d))) { *why = "Compression not cached, skipping sparse"; return false; }
+    if (!compression_cached) { *why = "Compression not cached, skipping sparse"; return false; }
     if (d.dtype != 0 && d.dtype != 1) { *why = "Only f16 / bf16 have a sparse kernel"; return false; }
     if (d.K % 64 != 0 || d.M % 8 != 0) { *why = "Shape not supported by the sparse kernel"; return false; }
     return true;
@@ -431,11 +601,16 @@ class Selector {
     return t;
   }
 
-  // Weight = desc.M x desc.K (the sparse operand), activations = desc.N tokens.
-  bool benchmark(const sf_matmul_desc& d, double* dense_ms, double* sparse_ms) {
+  // Weight = desc.M x desc.K (the sparse operand), activations = desc.N tokens.  Caller-provided
+  // device matrices are used when all three are given (with the cached compressed form of the weight
+  // when there is one); otherwise synthetic buffers, filled like the reference dispatcher's
+  // (dispatch/kernel_dispatcher.cpp:105-131).
+  bool benchmark(const sf_matmul_desc& d, const void* a_user, const void* x_user, void* y_user,
+                 const CompressedValue& cached, double* dense_ms, double* sparse_ms) {
     int err = kOk;
     DeviceState* s = device_state(&err);
     if (!s) return false;
+    const bool user = a_user && x_user && y_user;
     const size_t wb = static_cast<size_t>(d.M) * d.K * 2, xb = static_cast<size_t>(d.N) * d.K * 2,
                  yb = static_cast<size_t>(d.N) * d.M * 2, flush_bytes = 256u << 20;
     void *w = nullptr, *x = nullptr, *y = nullptr, *vals = nullptr, *meta = nullptr, *flush = nullptr;
@@ -443,27 +618,42 @@ class Selector {
       for (void* p : {w, x, y, vals, meta, flush})
         if (p) cudaFree(p);
     };
-    if (cudaMalloc(&w, wb) || cudaMalloc(&x, xb) || cudaMalloc(&y, yb) ||
-        cudaMalloc(&vals, values_bytes(d.M, d.K)) || cudaMalloc(&meta, meta_bytes(d.M, d.K)) ||
-        cudaMalloc(&flush, flush_bytes)) {
+    bool alloc_ok = cudaMalloc(&flush, flush_bytes) == cudaSuccess;
+    if (alloc_ok && !user)
+      alloc_ok = cudaMalloc(&w, wb) == cudaSuccess && cudaMalloc(&x, xb) == cudaSuccess &&
+                 cudaMalloc(&y, yb) == cudaSuccess;
+    if (alloc_ok && !cached.values)
+      alloc_ok = cudaMalloc(&vals, values_bytes(d.M, d.K)) == cudaSuccess &&
+                 cudaMalloc(&meta, meta_bytes(d.M, d.K)) == cudaSuccess;
+    if (!alloc_ok) {
       cudaGetLastError();
       free_all();
       return false;
     }
-    {  // weight pattern 1,1,0,0 ; activations 1.0 (same synthetic fill as the reference dispatcher)
+    if (!user) {  // weight pattern 1,1,0,0 ; activations 1.0
       const uint16_t one = d.dtype == 1 ? 0x3F80 : 0x3C00;
       std::vector<uint16_t> hw(static_cast<size_t>(d.M) * d.K), hx(static_cast<size_t>(d.N) * d.K, one);
       for (size_t i = 0; i < hw.size(); ++i) hw[i] = (i & 3) < 2 ? one : 0;
       cudaMemcpy(w, hw.data(), wb, cudaMemcpyHostToDevice);
       cudaMemcpy(x, hx.data(), xb, cudaMemcpyHostToDevice);
     }
+    const void* wsrc = user ? a_user : w;
+    const void* xsrc = user ? x_user : x;
+    void* ydst = user ? y_user : y;
     cudaStream_t st = nullptr;
-    PruneArgs pa{};
-    pa.dense = w; pa.rows = d.M; pa.K = d.K; pa.ld = d.K; pa.fmt = d.dtype; pa.tie = kTieHigh;
-    pa.values = vals; pa.meta = meta;
-    bool sparse_ok = launch_prune_compress(pa, st) == kOk;
+    bool sparse_ok = true;
+    const void* use_vals = cached.values;
+    const void* use_meta = cached.meta;
+    if (!use_vals) {
+      PruneArgs pa{};
+      pa.dense = wsrc; pa.rows = d.M; pa.K = d.K; pa.ld = d.K; pa.fmt = d.dtype; pa.tie = kTieHigh;
+      pa.values = vals; pa.meta = meta;
+      sparse_ok = launch_prune_compress(pa, st) == kOk;
+      use_vals = vals;
+      use_meta = meta;
+    }
     SparseGemmArgs ga{};
-    ga.x = x; ga.values = vals; ga.meta = meta; ga.y = y; ga.status = s->status;
+    ga.x = xsrc; ga.values = use_vals; ga.meta = use_meta; ga.y = ydst; ga.status = s->status;
     ga.m_tok = d.N; ga.n_out = d.M; ga.K = d.K; ga.ldx = d.K; ga.ldy = d.M; ga.fmt = d.dtype;
     ga.epi = kEpiStore; ga.act = kActNone; ga.num_sms = s->num_sms;
     if (sparse_ok) {
@@ -486,8 +676,8 @@ class Selector {
         // row-major Y[N,M] = X[N,K] . W[M,K]^T  ==  column-major Y^T[M,N] = W^T(op T) . X
         Timing td = time_it(
             [&] {
-              return cb.gemm_ex(h, 1 /*T*/, 0 /*N*/, d.M, d.N, d.K, &alpha, w, dt, d.K, x, dt, d.K, &beta,
-                                y, dt, d.M, 68 /*CUBLAS_COMPUTE_32F*/, -1 /*default algo*/) == 0;
+              return cb.gemm_ex(h, 1 /*T*/, 0 /*N*/, d.M, d.N, d.K, &alpha, wsrc, dt, d.K, xsrc, dt, d.K, &beta,
+                                ydst, dt, d.M, 68 /*CUBLAS_COMPUTE_32F*/, -1 /*default algo*/) == 0;
             },
             flush, flush_bytes, st);
         *dense_ms = td.mean_ms;
@@ -503,13 +693,20 @@ class Selector {
   std::mutex mu_;
   std::map<std::string, int> failures_;
   std::set<std::string> compressed_;
+  int64_t ctr_[kNumCounters] = {};
 };
 
 std::mutex g_mu;
 std::map<std::string, std::unique_ptr<Selector>> g_selectors;
 
+std::string resolve_path(const char* cache_path) {
+  if (cache_path) return cache_path;
+  const char* e = getenv("SPARSEFLOW_CACHE_DB");
+  return (e && *e) ? e : "kernel_cache.db";
+}
+
 Selector* selector_for(const char* cache_path) {
-  const std::string path = cache_path ? cache_path : "kernel_cache.db";
+  const std::string path = resolve_path(cache_path);
   std::lock_guard<std::mutex> lk(g_mu);
   auto& p = g_selectors[path];
   if (!p) p.reset(new Selector(path));
@@ -528,21 +725,68 @@ int32_t sf_select_kernel(const char* cache_path, const sf_matmul_desc* desc, con
   return selector_for(cache_path)->select(*desc, *gpu);
 }
 
-int32_t sf_cache_size(const char* cache_path) {
-  const std::string path = cache_path ? cache_path : "kernel_cache.db";
-  if (!sqlite_api().ok) {  // in-memory store lives inside the selector
-    KernelStore tmp(path);
-    (void)tmp;
-  }
-  KernelStore store(path);
-  if (store.persistent()) return store.size();
-  return 0;
+// Both go through the process's selector for that path, so the in-memory store (used when
+// libsqlite3 is absent) and the failure counts are covered too.
+int32_t sf_cache_size(const char* cache_path) { return selector_for(cache_path)->size(); }
+
+void sf_cache_clear(const char* cache_path) { selector_for(cache_path)->clear(); }
+
+int32_t sf_select_kernel_ex(const char* cache_path, const sf_matmul_desc* desc, const sf_gpu_info* gpu,
+                            const void* d_weight, const void* d_x, void* d_y) {
+  if (!desc || !gpu) return 0;
+  return selector_for(cache_path)->select(*desc, *gpu, d_weight, d_x, d_y);
 }
 
-void sf_cache_clear(const char* cache_path) {
-  const std::string path = cache_path ? cache_path : "kernel_cache.db";
-  KernelStore store(path);
-  store.clear();
+int32_t sf_compress_weight(const sf_matmul_desc* desc, const void* d_weight, const void** values,
+                           const void** meta) {
+  if (values) *values = nullptr;
+  if (meta) *meta = nullptr;
+  if (!desc || !d_weight || desc->sparsity_type != 1 || (desc->dtype != 0 && desc->dtype != 1)) return 0;
+  if (desc->M <= 0 || desc->K <= 0 || desc->K % 16 != 0) return 0;
+  int err = kOk;
+  if (!device_state(&err)) return 0;
+  CompressedKey key;
+  if (!make_compressed_key(*desc, d_weight, &key)) return 0;
+  CompressedValue v;
+  if (compressed_store().get(key, &v)) {
+    if (values) *values = v.values;
+    if (meta) *meta = v.meta;
+    return 1;
+  }
+  const size_t vb = values_bytes(desc->M, desc->K), mb = meta_bytes(desc->M, desc->K);
+  if (compressed_store().bytes() + vb + mb > CompressedStore::kMaxBytes) return 0;
+  if (cudaMalloc(&v.values, vb) != cudaSuccess || cudaMalloc(&v.meta, mb) != cudaSuccess) {
+    cudaGetLastError();
+    if (v.values) cudaFree(v.values);
+    return 0;
+  }
+  v.bytes = vb + mb;
+  PruneArgs pa{};
+  pa.dense = d_weight; pa.rows = desc->M; pa.K = desc->K; pa.ld = desc->K; pa.fmt = desc->dtype; pa.tie = kTieHigh;
+  pa.values = v.values; pa.meta = v.meta;
+  const bool ok = launch_prune_compress(pa, nullptr) == kOk && cudaStreamSynchronize(nullptr) == cudaSuccess &&
+                  compressed_store().put(key, v);
+  if (!ok) {
+    cudaFree(v.values);
+    cudaFree(v.meta);
+    return 0;
+  }
+  if (values) *values = v.values;
+  if (meta) *meta = v.meta;
+  return 1;
+}
+
+int32_t sf_compressed_cache_count(void) { return static_cast<int32_t>(compressed_store().count()); }
+uint64_t sf_compressed_cache_bytes(void) { return compressed_store().bytes(); }
+void sf_compressed_cache_clear(void) { compressed_store().clear(); }
+
+int32_t sf_get_counters(const char* cache_path, int64_t* out, int32_t n) {
+  if (!out || n <= 0) return 0;
+  int64_t c[kNumCounters];
+  selector_for(cache_path)->counters(c);
+  const int m = n < kNumCounters ? n : kNumCounters;
+  for (int i = 0; i < m; ++i) out[i] = c[i];
+  return m;
 }
 
 void sf_note_compressed(const char* cache_path, const sf_matmul_desc* desc) {

@@ -95,9 +95,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait.  `err` is a CTA-shared flag: once any thread of the CTA sets it every later wait
 // returns false at once, so all roles fall through to the teardown.  `gstatus` (global) receives the
-// first failure for the host to read.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* err,
-                                          int* gstatus, int where) {
+// first failure for the host to read.  `limit_ns` is the time after which the wait gives up.
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* err,
+                                                int* gstatus, int where, unsigned long long limit_ns) {
   // Polls only, first: reading %globaltimer costs on the order of a pipeline stage (measured: a
   // wait that consulted it on every miss put ~190 ns under every K step of every kernel), so the
   // clock and the error flag are looked at once per 64 missed polls.
@@ -108,13 +108,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*err) return false;
       const unsigned long long now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) {
+      else if (now - t0 > limit_ns) {
         *err = 1;
         atomicCAS(gstatus, 0, (kStatusWaitTimeout << 8) | where);
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* err,
+                                          int* gstatus, int where) {
+  return mbar_wait_limit(bar, parity, err, gstatus, where, kWaitLimitNs);
 }
 
 // ---------------------------------------------------------------- proxies / fences

@@ -10,10 +10,12 @@
 //     229 for 512x208 (RS = 2).  Shared-memory reads per MMA drop the same way (each SM reads half
 //     of the token tile);
 //   * the even CTA of the pair issues every MMA; completion is signalled to both CTAs;
-//   * accumulators (RS x BN fp32 columns, 128 lanes per CTA) are single-buffered: tensor memory
-//     has 512 columns and the metadata needs some.  The epilogue streams them out in 16-column
-//     chunks with the next chunk's tcgen05.ld in flight, and hands the accumulators back right
-//     after the last load; its stores overlap the next tile's main loop.
+//   * accumulators (RS x BN fp32 columns, 128 lanes per CTA) live in tensor memory, which has 512
+//     columns of which the metadata ring needs 16-32.  With RS = 1 and BN <= 240 two accumulators
+//     fit (2 x 240 + 16 = 496): the MMA stream of tile i+1 fills one while the epilogue drains the
+//     other, so the epilogue is off the critical path.  BN = 256 and the RS = 2 tiles have a single
+//     accumulator set; their epilogue hands it back right after its last tensor-memory load and
+//     only its conversion and stores overlap the next tile's main loop.
 //
 // 10 warps: warp 0 = TMA producer, warp 1 = MMA issuer / tensor-memory owner, warps 2..9 = epilogue.
 // All loads are plain per-CTA TMA copies; nothing here reads another GPU's memory.
@@ -189,9 +191,12 @@ struct PairCfg {
   // (shared memory and tensor-memory columns) has STAGES/2 + 1 slots.  A slot is reused
   // STAGES + 2 stages after it was written, i.e. after the stage barrier that guards it.
   static constexpr int E_STAGES = (BK == 128) ? STAGES : STAGES / 2 + 1;
-  static constexpr int E_COL0 = RS * BN;          // metadata columns start after the accumulators
   static constexpr int E_COLS_STAGE = 4 * RS;
-  static constexpr int TMEM_USED = RS * BN + E_COLS_STAGE * E_STAGES;
+  // accumulator sets: two when they fit beside the metadata ring (RS = 1, BN <= 240)
+  static constexpr int ACC_COLS = RS * BN;
+  static constexpr int ACC_BUFS = (RS == 1 && 2 * ACC_COLS + E_COLS_STAGE * E_STAGES <= 512) ? 2 : 1;
+  static constexpr int E_COL0 = ACC_BUFS * ACC_COLS;   // metadata columns start after the accumulators
+  static constexpr int TMEM_USED = ACC_BUFS * ACC_COLS + E_COLS_STAGE * E_STAGES;
   static constexpr int TMEM_COLS = TMEM_USED <= 128 ? 128 : TMEM_USED <= 256 ? 256 : 512;
   static constexpr int OFF_A = 0;
   static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
@@ -206,12 +211,14 @@ struct PairCfg {
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
   static constexpr int EPI_WARPS = 8;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
-  // 8 epilogue warps = 4 lane quadrants x 2: with RS = 1 the two warps of a quadrant split the
-  // columns, with RS = 2 each takes one accumulator.
-  static constexpr int COLS_PER_WARP = (RS == 1) ? BN / 2 : BN;
+  // 8 epilogue warps = 4 lane quadrants x 2.  RS = 2: each takes one accumulator.  RS = 1: each
+  // loads 128 columns, the first [0, 128), the second [BN - 128, BN); the second one stores only
+  // what the first does not cover, i.e. it skips its first (256 - BN) / 16 chunks.
+  static constexpr int COLS_PER_WARP = (RS == 1) ? 128 : BN;
+  static constexpr int SKIP_CHUNKS = (RS == 1) ? (256 - BN) / 16 : 0;
   static_assert(RS == 1 || RS == 2, "RS");
   static_assert(BK == 128 || STAGES % 2 == 0, "BK = 64 needs an even stage count");
-  static_assert(BN % 16 == 0 && BN <= 256, "BN");
+  static_assert(BN % 16 == 0 && BN <= 256 && (RS == 2 || BN >= 128), "BN");
   static_assert(HALF_N % 8 == 0, "token half must be whole swizzle atoms");
   static_assert(COLS_PER_WARP % 16 == 0, "epilogue chunking");
   static_assert(TMEM_USED <= 512, "tmem");
@@ -316,9 +323,9 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   const uint32_t bar_full = smem_u32(bars);                 // used in the even CTA only
   const uint32_t bar_empty = bar_full + 8 * C::STAGES;      // both CTAs
-  const uint32_t bar_accf = bar_empty + 8 * C::STAGES;      // both CTAs
-  const uint32_t bar_acce = bar_accf + 8;                   // even CTA only
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + 8 * (2 * C::STAGES + 2));
+  const uint32_t bar_accf = bar_empty + 8 * C::STAGES;      // both CTAs, one per accumulator set
+  const uint32_t bar_acce = bar_accf + 16;                  // even CTA only, one per accumulator set
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + 8 * (2 * C::STAGES + 4));
   volatile int* err = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -338,8 +345,10 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    mbar_init(bar_accf, 1);
-    mbar_init(bar_acce, 2 * C::EPI_WARPS);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_accf + 8 * b, 1);
+      mbar_init(bar_acce + 8 * b, 2 * C::EPI_WARPS);
+    }
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
@@ -400,13 +409,16 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
     if (leader && elect_one()) {
       const uint32_t idesc = make_idesc_f16(256, C::BN, p.fmt, true);
       int s = 0, es = 0;
-      uint32_t ph = 0, aph = 0;
+      uint32_t ph = 0;
       uint32_t e_cols = 0;
       bool ok = true;
-      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
-        ok = mbar_wait(bar_acce, aph ^ 1, err, p.status, 3);
+      uint32_t it = 0;    // tiles done by this pair: accumulator set = it % ACC_BUFS, its use count = it / ACC_BUFS
+      for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++it) {
+        const uint32_t as = (C::ACC_BUFS == 2) ? (it & 1u) : 0u;
+        const uint32_t use = (C::ACC_BUFS == 2) ? (it >> 1) : it;
+        const uint32_t d_base = tmem_base + as * C::ACC_COLS;
+        ok = mbar_wait(bar_acce + 8 * as, (use & 1u) ^ 1u, err, p.status, 3);
         if (!ok) break;
-        aph ^= 1;
         tc_fence_after();
         for (int kt = 0; kt < k_iters; ++kt) {
           ok = mbar_wait(bar_full + 8 * s, ph, err, p.status, 2);
@@ -434,7 +446,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
               const uint32_t a_sub = a_addr + rs * C::A_SUB_BYTES + kb * 32;
               const uint64_t adesc = (C::BK == 64) ? make_smem_desc(a_sub, 16, 512, kSw64)
                                                    : make_smem_desc(a_sub, 16, 1024, kSw128);
-              tc_mma_sp_f16_pair(tmem_base + rs * C::BN, adesc, bdesc,
+              tc_mma_sp_f16_pair(d_base + rs * C::BN, adesc, bdesc,
                                  tmem_base + e_cols + 4 * rs + (ecol & ~1), idesc | (ecol & 1),
                                  (kt > 0 || kb > 0) ? 1u : 0u);
             }
@@ -443,7 +455,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
           if (++s == C::STAGES) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
-        tc_commit_pair(bar_accf);
+        tc_commit_pair(bar_accf + 8 * as);
       }
     }
   } else {
@@ -451,26 +463,29 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
     const int q = warp & 3;                 // lane quadrant
     const int w2 = (warp - 2) >> 2;         // 0 / 1: column half (RS = 1) or accumulator (RS = 2)
     const int acc = (C::RS == 1) ? 0 : w2;
-    const int col0 = (C::RS == 1) ? w2 * C::COLS_PER_WARP : 0;
-    const uint32_t leader_acce = mapa_u32(bar_acce, 0);
+    const int col0 = (C::RS == 1) ? w2 * (C::BN - 128) : 0;
+    const int c_begin = (C::RS == 1) ? w2 * C::SKIP_CHUNKS : 0;   // first chunk this warp stores
+    const uint32_t leader_acce0 = mapa_u32(bar_acce, 0);
     const uint64_t pol_stream = l2_policy_evict_first();
-    uint32_t aph = 0;
     bool ok = true;
     constexpr int NCH = C::COLS_PER_WARP / 16;
     const bool upper = lane >= 16;
-    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+    uint32_t it = 0;
+    for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++it) {
       int m_blk, n_blk;
       tile_coords(tile, p, m_blk, n_blk);
+      const uint32_t as = (C::ACC_BUFS == 2) ? (it & 1u) : 0u;
+      const uint32_t use = (C::ACC_BUFS == 2) ? (it >> 1) : it;
+      const uint32_t leader_acce = leader_acce0 + 8 * as;
       {
-        bool w = mbar_wait(bar_accf, aph, err, p.status, 4);
+        bool w = mbar_wait(bar_accf + 8 * as, use & 1u, err, p.status, 4);
         ok = __all_sync(0xffffffffu, w);
       }
       if (!ok) break;
-      aph ^= 1;
       tc_fence_after();
       const int row_w = m_blk * C::ROWS_TILE + static_cast<int>(rank) * C::ROWS_CTA + acc * 128 + q * 32;
       const int tok_w = n_blk * C::BN + col0;
-      const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * C::BN + col0;
+      const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * C::ACC_COLS + acc * C::BN + col0;
       uint16_t* ycol;
       bool col_ok;
       float bias_v = 0.f;
@@ -512,6 +527,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
         const int out_x = (C::EPI == kEpiSwiGLU) ? row_w / 2 : row_w;   // first output column of this warp
 #pragma unroll
         for (int c = 0; c < NCOL / 16; ++c) {
+          if (c < c_begin) continue;                   // columns the other warp of this quadrant stores
           const uint32_t stage = stage0 + (c & 1) * C::D_BUF_BYTES;
           if (lane == 0) tma_store_wait_read<1>();     // the buffer's previous store has read it
           __syncwarp();
@@ -652,16 +668,27 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
 }
 
 // Tile choice.  Cost of a launch in units of "token columns of a 256-row tile at K = 4096":
-// waves x (MMA columns per tile + exposed epilogue).  The 256-row kernel drains its accumulator
-// through registers (about 30 units exposed); the 512-row kernel streams two accumulators out in
-// chunks (about 90 units) but does twice the work per tile and can hit a whole number of waves
-// where 256-row tiles do not (e.g. a 4096-row weight at 4096 tokens: 144 tiles on 74 SM pairs).
+// waves x (MMA columns per tile + exposed epilogue).  The 256-row x 256-token tile drains its single
+// accumulator through registers (about 30 units exposed); 256-row tiles of 192..240 tokens have two
+// accumulators (epilogue hidden, a few units of hand-over); the 512-row kernel streams two
+// accumulators out in chunks (about 90 units) but does twice the work per tile.  Which one wins is
+// mostly a matter of wave quantisation on the 74 SM pairs (e.g. a 4096-row weight at 4096 tokens:
+// 256 tiles of 256 x 256 = 3.46 waves, 288 tiles of 256 x 240 = 3.89 waves).
 int pick_pair_variant_impl(int n_out, int m_tok, int K, int pairs) {
   const double kscale = 4096.0 / (K > 0 ? K : 4096);
   auto waves = [&](long tiles) { return static_cast<double>((tiles + pairs - 1) / pairs); };
-  const long t1 = static_cast<long>((n_out + 255) / 256) * ((m_tok + 255) / 256);
+  const long rows256 = (n_out + 255) / 256;
+  const long t1 = rows256 * ((m_tok + 255) / 256);
   double best_cost = waves(t1) * (256.0 + 30.0 * kscale);
   int best = 1256;
+  {
+    const int cands[4] = {240, 224, 208, 192};
+    for (int bn : cands) {
+      const long t = rows256 * ((m_tok + bn - 1) / bn);
+      const double c = waves(t) * (bn + 8.0 * kscale);
+      if (c < best_cost * 0.99) { best_cost = c; best = 1000 + bn; }
+    }
+  }
   if (n_out >= 512) {
     const int cands[4] = {192, 208, 224, 240};
     for (int bn : cands) {
@@ -675,12 +702,16 @@ int pick_pair_variant_impl(int n_out, int m_tok, int K, int pairs) {
 
 template <int EPI>
 int dispatch_pair(const SparseGemmArgs& a, cudaStream_t stream) {
-  // force_bn: 1256 = 256-row tiles with 256 tokens; 2192 / 2208 / 2224 / 2240 =
-  // 512-row tiles with that many tokens.  0 = automatic.
+  // force_bn: 1256 / 1240 / 1224 / 1208 / 1192 = 256-row tiles with that many tokens;
+  // 2192 / 2208 / 2224 / 2240 = 512-row tiles with that many tokens.  0 = automatic.
   int v = a.force_bn;
   if (v == 0) v = pick_pair_variant_impl(a.n_out, a.m_tok, a.K, a.num_sms / 2);
   switch (v) {
     case 1256: return launch_pair_cfg<PairCfg<256, 128, 4, 1, EPI>>(a, stream);
+    case 1240: return launch_pair_cfg<PairCfg<240, 128, 4, 1, EPI>>(a, stream);
+    case 1224: return launch_pair_cfg<PairCfg<224, 128, 4, 1, EPI>>(a, stream);
+    case 1208: return launch_pair_cfg<PairCfg<208, 128, 4, 1, EPI>>(a, stream);
+    case 1192: return launch_pair_cfg<PairCfg<192, 128, 4, 1, EPI>>(a, stream);
     case 2192: return launch_pair_cfg<PairCfg<192, 64, 6, 2, EPI>>(a, stream);
     case 2208: return launch_pair_cfg<PairCfg<208, 64, 6, 2, EPI>>(a, stream);
     case 2224: return launch_pair_cfg<PairCfg<224, 64, 6, 2, EPI>>(a, stream);

@@ -63,6 +63,10 @@ class SparseFlowLinear(nn.Module):
         _require_cuda_16bit(weight_fp16, "weight_fp16")
         if bias_fp16 is not None:
             _require_cuda_16bit(bias_fp16, "bias_fp16")
+            if bias_fp16.dtype != weight_fp16.dtype:
+                raise ValueError(f"bias dtype {bias_fp16.dtype} != weight dtype {weight_fp16.dtype}")
+            if bias_fp16.numel() != weight_fp16.shape[0]:
+                raise ValueError(f"bias has {bias_fp16.numel()} elements, weight has {weight_fp16.shape[0]} rows")
 
         W = weight_fp16.contiguous()
         self.register_buffer("W_original", W, persistent=True)

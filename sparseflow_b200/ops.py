@@ -176,6 +176,26 @@ def decompress_24(cw: Compressed24) -> torch.Tensor:
     return out
 
 
+def _kernel_ready(x: torch.Tensor) -> torch.Tensor:
+    """The kernels read activations through TMA: unit inner stride, row pitch a multiple of 8 elements,
+    16-byte aligned base.  A view that breaks one of these (a column slice, an odd offset) is copied,
+    as the reference's call sites do unconditionally (sparseflow/nn/sparseflow_linear.py:122-124)."""
+    if x.stride(1) != 1 or (x.shape[0] > 1 and x.stride(0) % 8 != 0) or x.data_ptr() % 16 != 0:
+        return x.contiguous()
+    return x
+
+
+def _check_bias(bias: torch.Tensor, x: torch.Tensor, rows: int) -> torch.Tensor:
+    """The epilogue reads `rows` bias values in the GEMM's own 16-bit type."""
+    if not bias.is_cuda or bias.device != x.device:
+        raise ValueError(f"bias must be a CUDA tensor on {x.device}, got {bias.device}")
+    if bias.dtype != x.dtype:
+        raise ValueError(f"bias dtype {bias.dtype} != activation dtype {x.dtype}")
+    if bias.numel() != rows:
+        raise ValueError(f"bias has {bias.numel()} elements, weight has {rows} rows")
+    return bias.contiguous().view(-1)
+
+
 def sparse_gemm(x: torch.Tensor, cw: Compressed24, bias: Optional[torch.Tensor] = None,
                 act: Optional[str] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y[M, N] = act(x[M, K] . W^T + bias)."""
@@ -184,8 +204,9 @@ def sparse_gemm(x: torch.Tensor, cw: Compressed24, bias: Optional[torch.Tensor] 
         raise ValueError(f"Expected last dim {cw.K}, got {tuple(x.shape)}")
     if x.dtype != cw.dtype:
         raise ValueError(f"x dtype {x.dtype} != weight dtype {cw.dtype}")
-    if x.stride(1) != 1:
-        x = x.contiguous()
+    x = _kernel_ready(x)
+    if bias is not None:
+        bias = _check_bias(bias, x, cw.rows)
     M = x.shape[0]
     with _on(x.device):
         if out is None:
@@ -206,8 +227,7 @@ def sparse_gemm_swiglu(x: torch.Tensor, cw_gu: Compressed24, out: Optional[torch
         raise ValueError("weight was not built with compress_gate_up")
     if x.dim() != 2 or x.shape[1] != cw_gu.K or x.dtype != cw_gu.dtype:
         raise ValueError("shape / dtype mismatch")
-    if x.stride(1) != 1:
-        x = x.contiguous()
+    x = _kernel_ready(x)
     M, I = x.shape[0], cw_gu.rows // 2
     with _on(x.device):
         if out is None:

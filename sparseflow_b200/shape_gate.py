@@ -39,7 +39,36 @@ def default_ranges() -> Dict[str, GateRange]:
                           decode_hi=int(dispatch.DECODE_MAX_M[c])) for op, c in _OP_CLASS.items()}
 
 
-DEFAULT_RANGES: Dict[str, GateRange] = default_ranges()
+class _LiveRanges(dict):
+    """``DEFAULT_RANGES`` of the reference's module, but read from the gate table at every lookup so that
+    ``dispatch.reload_gate()`` takes effect here too."""
+
+    def get(self, op, default=None):
+        return default_ranges().get(op, default)
+
+    def __getitem__(self, op):
+        return default_ranges()[op]
+
+    def __contains__(self, op):
+        return op in _OP_CLASS
+
+    def __iter__(self):
+        return iter(_OP_CLASS)
+
+    def __len__(self):
+        return len(_OP_CLASS)
+
+    def items(self):
+        return default_ranges().items()
+
+    def keys(self):
+        return default_ranges().keys()
+
+    def values(self):
+        return default_ranges().values()
+
+
+DEFAULT_RANGES: Dict[str, GateRange] = _LiveRanges()
 
 
 class ShapeOverrides:

@@ -47,8 +47,8 @@ def _run(R, K, M, dt, bn=0, sigma=0.02, wseed=1, xseed=1234, bias=False, act=Non
 
 
 @pytest.mark.parametrize("bn,R,K,M", [(64, 128, 64, 64), (128, 128, 128, 128), (256, 128, 256, 256),
-                                      (1256, 256, 256, 256), (2208, 512, 256, 208),
-                                      (2240, 1024, 192, 240)])
+                                      (1256, 256, 256, 256), (1240, 512, 256, 240), (1192, 256, 192, 192),
+                                      (2208, 512, 256, 208), (2240, 1024, 192, 240)])
 def test_identity_activations_reproduce_pruned_weight_exactly(bn, R, K, M):
     dt = "bf16"
     w = seeded_weight(R, K, dt, 3)
@@ -61,10 +61,19 @@ def test_identity_activations_reproduce_pruned_weight_exactly(bn, R, K, M):
     assert (bits_of(y)[:n].T == o.prune_24(w, dt)["pruned"][:, :n]).all()
 
 
-@pytest.mark.parametrize("bn", [32, 64, 128, 192, 256, 1256, 2192, 2208, 2224, 2240])
+@pytest.mark.parametrize("bn", [32, 64, 128, 192, 256, 1256, 1240, 1224, 1208, 1192, 2192, 2208, 2224, 2240])
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
 def test_every_kernel_variant_ragged(bn, dt):
     y, ref = _run(392, 512, 300, dt, bn=bn)
+    assert o.rel_err_metrics(y, ref)["floor"] <= REL_TOL
+
+
+@pytest.mark.parametrize("bn", [1240, 1224, 1208, 1192])
+def test_two_accumulator_pair_tiles_many_tiles_per_pair(bn):
+    """The 256-row tiles with two accumulator sets, on a problem with more tiles than SM pairs (5 row tiles
+    x 9-11 token tiles on 74 pairs would be one tile each; 24 row tiles x 9-11 gives every pair 3-4 tiles), so
+    both accumulator sets and their phase bits are reused; bias + activation in the epilogue."""
+    y, ref = _run(6144 - 8, 256, 2000, "bf16", bn=bn, bias=True, act="relu")
     assert o.rel_err_metrics(y, ref)["floor"] <= REL_TOL
 
 
@@ -89,7 +98,7 @@ def test_small_m_kernel_mistral_down_shape():
     assert o.rel_err_metrics(y, ref)["floor"] <= REL_TOL
 
 
-@pytest.mark.parametrize("bn", [128, 1256, 2208])
+@pytest.mark.parametrize("bn", [128, 1256, 1240, 2208])
 @pytest.mark.parametrize("act", [None, "relu", "silu", "gelu"])
 def test_bias_and_activation_epilogues(bn, act):
     y, ref = _run(256, 512, 200, "f16", bn=bn, bias=True, act=act)
@@ -143,7 +152,7 @@ def test_split_k_auto_dispatch_on_few_row_tiles(R, K, M):
     assert o.rel_err_metrics(o.to_f32(bits_of(y1), dt), ref)["floor"] <= REL_TOL
 
 
-@pytest.mark.parametrize("bn", [0, 2240])
+@pytest.mark.parametrize("bn", [0, 1240, 2240])
 def test_pair_kernel_l2_band_tile_order(bn):
     """Enough token tiles at K = 8192 that the prefill kernel walks them in more than one L2 band
     (12-13 token tiles, bands of 6-7), with ragged rows and tokens."""

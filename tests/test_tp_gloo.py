@@ -76,3 +76,15 @@ def test_shard_bounds_errors():
         parallel.shard_bounds(24, 4, 0)          # shards of 6 are not multiples of 4
     assert parallel.shard_bounds(11008, 8, 7) == (9632, 11008)
     assert parallel.padded_width(1376) == 1408 and parallel.padded_width(3584) == 3584
+
+
+def test_token_blocks_partition_the_batch():
+    """Owner blocks of the exchange step: multiples of 16 rows, consecutive, covering [0, M) exactly once."""
+    for tp in (2, 4, 8):
+        for M in (1, 15, 16, 17, 40, 100, 1000, 4096, 8191):
+            mo = parallel.block_rows(M, tp)
+            assert mo % 16 == 0 and mo * tp >= M and (mo - 16) * tp < M
+            spans = [parallel.owned_rows(M, tp, r) for r in range(tp)]
+            assert spans[0][0] == 0 and spans[-1][1] == M
+            for (a, b), (c, d) in zip(spans, spans[1:]):
+                assert b == c and a <= b and c <= d

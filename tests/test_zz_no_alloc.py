@@ -41,6 +41,9 @@ def test_noalloc_matches_regular_entry_point_twice():
         assert L.sfb200_ffn_forward_noalloc(C.byref(W), x.data_ptr(), H, got.data_ptr(), H, M, st) == 0
         torch.cuda.synchronize()
         assert torch.equal(got, want)              # same kernels, same bits: tolerance 0
+        # this entry point reports device-side failures in a word of its own, read without allocating
+        word = C.c_int(-1)
+        assert L.sfb200_noalloc_device_status(C.byref(word)) == 0 and word.value == 0
     assert ops.device_status() == 0
 
 

@@ -25,3 +25,25 @@ def seeded_act(M, K, dtype, seed):
     g = torch.Generator(device="cpu").manual_seed(seed)
     x = torch.randn(M, K, generator=g, dtype=torch.float32)
     return o.from_f32(x.numpy(), dtype)
+
+
+def big_gemm_ref(x_bits: np.ndarray, w_pruned_bits: np.ndarray, dtype: str) -> np.ndarray:
+    """``oracle.gemm_ref`` (fp32 matmul on the pruned weights, experiments/gen_pruned_ref.py:5-8) with the
+    product itself done by torch's multi-threaded CPU sgemm, for the full-size configurations."""
+    import oracle as o
+    x = torch.from_numpy(o.to_f32(x_bits, dtype))
+    w = torch.from_numpy(o.to_f32(w_pruned_bits, dtype))
+    return (x @ w.t()).numpy()
+
+
+def big_ffn_ref(x_bits, wg_pruned, wu_pruned, wd_pruned, dtype: str, round_gate_up: bool = False) -> dict:
+    """``oracle.ffn_ref`` with the same rounding points, matmuls through ``big_gemm_ref``."""
+    import oracle as o
+    g = big_gemm_ref(x_bits, wg_pruned, dtype)
+    u = big_gemm_ref(x_bits, wu_pruned, dtype)
+    if round_gate_up:
+        g = o.to_f32(o.from_f32(g, dtype), dtype)
+        u = o.to_f32(o.from_f32(u, dtype), dtype)
+    h = o.from_f32(o.silu_mul_ref(g, u), dtype)
+    out = big_gemm_ref(h, wd_pruned, dtype)
+    return dict(hidden=h, out=o.from_f32(out, dtype), out_f32=out)
