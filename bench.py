@@ -57,9 +57,13 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama7b_ffn", choices=sorted(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=0, help="override the token count")
-    ap.add_argument("--tp", default="fused", choices=["fused", "scatter", "nccl"],
-                    help="N > 1: exchange step in one kernel through NVSwitch (fused), scatter epilogue + reduce kernel "
-                         "over peer stores (scatter), or NCCL all-reduce (nccl)")
+    ap.add_argument("--tp", default="push", choices=["push", "switch", "nccl"],
+                    help="N > 1: reduce-scatter by peer stores in the down GEMM's epilogue + one reduce/all-gather kernel "
+                         "(push), the exchange pulled through NVSwitch in one kernel (switch), or NCCL all-reduce (nccl)")
+    ap.add_argument("--tp-partial", default="fp32", choices=["fp32", "16bit"],
+                    help="N > 1, push / switch: type of the per-rank partial sums that are exchanged (16bit halves the bytes of "
+                         "the reduction but rounds every partial; see FusedTensorParallelFFN)")
+    ap.add_argument("--tp-chunks", type=int, default=1, help="N > 1, switch: token chunks of the down GEMM / exchange pipeline")
     ap.add_argument("--tp-phases", action="store_true", help="N > 1: print per-phase device times to stderr")
     ap.add_argument("--chunks", type=int, default=1, help="token chunks for all-reduce overlap (N > 1, --tp nccl)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -538,13 +542,16 @@ def main():
 
     exchange = "none (single GPU)"
     ffn = None
-    if world > 1 and args.tp in ("fused", "scatter"):
+    if world > 1 and args.tp in ("push", "switch"):
         try:
-            ffn = parallel.FusedTensorParallelFFN(wg, wu, wd, max_tokens=M,
-                                                  exchange="auto" if args.tp == "fused" else "scatter")
-            exchange = ("one kernel per rank: barrier, in-switch reduction (multimem.ld_reduce), multimem.st of the finished block, barrier"
+            ffn = parallel.FusedTensorParallelFFN(wg, wu, wd, max_tokens=M, partial_dtype=args.tp_partial,
+                                                  chunks=args.tp_chunks, exchange=args.tp)
+            exchange = (f"{args.tp_partial} partial sums; per token chunk ({len(ffn._chunk_spans(M))} chunks, exchange of chunk c "
+                        "beside the down GEMM of chunk c+1) one kernel per rank: barrier, in-switch reduction "
+                        "(multimem.ld_reduce), multimem.st of the finished block, barrier"
                         if ffn.exchange == "switch" else
-                        "reduce-scatter in the down-GEMM epilogue (TMA stores to peer memory), all-gather in the reduction kernel")
+                        f"{args.tp_partial} partial sums; reduce-scatter by peer stores in the down GEMM's epilogue, then one kernel "
+                        "per rank: barrier, sum of the receive slots, peer stores of the finished block to every rank, barrier")
         except Exception as exc:      # symmetric memory unavailable on this box: NCCL path
             sys.stderr.write(f"fused tensor-parallel path unavailable ({exc!r}); using NCCL all-reduce\n")
             ffn = None
@@ -615,8 +622,7 @@ def main():
     launches = ffn.kernel_launches - launches0
     result = out if not fused_tp else res
     if fused_tp and args.tp_phases:       # after the timed region: ten more steps with events between the phases
-        names = (["gate_up_gemm", "down_gemm", "exchange"] if ffn.exchange == "switch" else
-                 ["gate_up_gemm", "down_gemm_scatter", "barrier_1", "reduce_allgather", "barrier_2"])
+        names = ["gate_up_gemm", "down_gemm_first_chunk", "exchange_and_remaining_chunks"]
         acc = [0.0] * len(names)
         for _ in range(10):
             evs = []
@@ -699,40 +705,43 @@ def main():
             ph = parity_object(out_host.to(dev), x_host, H, I, parity["rows_checked"])
             e2e["parity_chain"] = ph["chain"]
             parity["ok"] = parity["ok"] and ph["ok"]
-    elif fused_tp and ffn.exchange == "switch":
+    elif fused_tp:
         # every rank uploads ONLY its own token rows, the rows are replicated through the switch, and every rank
         # reads back ONLY the block it finished
         lo, hi = ffn.owned_rows(M)
         x_slice_host = x_host[lo:hi].clone().pin_memory()
         x_slice = torch.empty((hi - lo, H), dtype=dt, device=dev)
-        out_host = torch.empty((hi - lo, H), dtype=dt).pin_memory()
-        for _ in range(2):
+        mine = ffn.finished_rows(M)
+        out_hosts = [torch.empty((b - a, H), dtype=dt).pin_memory() for a, b in mine]
+
+        def e2e_step():
             x_slice.copy_(x_slice_host, non_blocking=True)
             r2 = ffn.forward_from_shards(x_slice, M)
-            out_host.copy_(r2[lo:hi], non_blocking=True)
+            for (a, b), oh in zip(mine, out_hosts):
+                oh.copy_(r2[a:b], non_blocking=True)
+        for _ in range(2):
+            e2e_step()
         barrier()
         e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
         l0 = ffn.kernel_launches
         e0.record()
         for _ in range(args.steps):
-            x_slice.copy_(x_slice_host, non_blocking=True)
-            r2 = ffn.forward_from_shards(x_slice, M)
-            out_host.copy_(r2[lo:hi], non_blocking=True)
+            e2e_step()
             torch.cuda.current_stream().synchronize()
         e1.record(); barrier()
         launches += ffn.kernel_launches - l0
         t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item()) / args.steps
-        same = torch.tensor([int(torch.equal(out_host.to(dev), result[lo:hi]))], device=dev)
+        same = torch.tensor([int(all(torch.equal(oh.to(dev), result[a:b]) for (a, b), oh in zip(mine, out_hosts)))], device=dev)
         dist.all_reduce(same, op=dist.ReduceOp.MIN)
         e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": M * H * 2, "d2h_bytes_per_step": M * H * 2, "ms_per_step": e2e_ms,
-               "call": "each rank: H2D of its own token rows, FusedTensorParallelFFN.forward_from_shards (all-gather through "
-                       "the switch + FFN + exchange), D2H of the block it finished; bytes are totals over ranks",
+               "call": "each rank: H2D of its own token rows, FusedTensorParallelFFN.forward_from_shards (all-gather over "
+                       "NVLink + FFN + exchange), D2H of the block it finished; bytes are totals over ranks",
                "equals_device_path": bool(same.item())}
     else:
-        # NCCL / scatter path: every rank copies the replicated x in and rank 0 reads the result back
+        # NCCL path: every rank copies the replicated x in and rank 0 reads the result back
         out_host = torch.empty((M, H), dtype=dt).pin_memory()
         barrier()
         e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)

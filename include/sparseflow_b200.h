@@ -118,6 +118,13 @@ SFB200_API int sfb200_sparse_gemm(const void* x, int ldx, const void* values, co
                                   void* y, int ldy, int M, int N, int K, int dtype,
                                   const void* bias, int act, void* stream);
 
+/* Same with FLOAT output y[M, N] (row pitch ldy floats): the fp32 accumulators (+ bias, activation) are stored
+ * unrounded.  For the partial sums of a row-parallel GEMM, whose rounding to 16 bits should happen once, after
+ * the sum over ranks.  Prefill kernel only (any M; small M runs it on one tile).  No counterpart upstream. */
+SFB200_API int sfb200_sparse_gemm_f32out(const void* x, int ldx, const void* values, const void* meta, float* y,
+                                         int ldy, int M, int N, int K, int dtype, const void* bias, int act,
+                                         void* stream);
+
 /*
  * H[M, I] = silu(X . Wg^T) * (X . Wu^T) with the fused gate|up weight produced by
  * sfb200_prune_compress_gate_up (2*I rows).  One GEMM, SiLU.mul in the epilogue: replaces the
@@ -162,53 +169,55 @@ SFB200_API int sfb200_ffn_forward_host(const sfb200_ffn_weights* w, const void* 
                                        void* out_host, int M, void* stream);
 
 /*
- * Tensor-parallel building blocks (no counterpart in the reference, which has no distributed code).
+ * Tensor-parallel building blocks (no counterpart in the reference, which has no distributed code).  One process per
+ * GPU; buffers that other ranks touch live in peer-mapped memory (e.g. torch symmetric memory).  The FFN shards as
+ * column-parallel gate/up and row-parallel down; the row-parallel GEMM leaves partial sums that must be added across
+ * ranks (reduce-scatter) and the finished token blocks replicated (all-gather).
+ *
  * Row-parallel GEMM with the reduce-scatter fused into its epilogue: rank r computes its partial
- * Y_r[M, N] = X_r . W_r^T and stores token block o (tok_per_owner tokens, a multiple of 16) straight
- * into peer_slots[o], rank o's receive slot for rank r ([tok_per_owner, N], peer-mapped memory, e.g.
- * a torch symmetric-memory buffer).  peer_slots is a HOST array of tp device pointers.  tp <= 8.
+ * Y_r[M, N] = X_r . W_r^T and stores token block o (tok_per_owner tokens, a multiple of 16) straight into
+ * peer_slots[o], rank o's receive slot for rank r ([tok_per_owner, N]; FLOAT when slots_f32, else `dtype`), with plain
+ * stores over NVLink that overlap the GEMM tile by tile.  peer_slots is a HOST array of tp device pointers.  tp <= 8.
+ * With float slots the partial sums are rounded to 16 bits only once, after they have been added.
  */
 SFB200_API int sfb200_sparse_gemm_scatter(const void* x, int ldx, const void* values, const void* meta,
-                                          void* const* peer_slots, int tp, int tok_per_owner, int M, int N,
-                                          int K, int dtype, void* stream);
+                                          void* const* peer_slots, int tp, int tok_per_owner, int slots_f32, int M,
+                                          int N, int K, int dtype, void* stream);
 /*
- * slots[tp][rows, cols] (local) are summed in fp32 (+ bias) and the result is written to
- * peer_out_blocks[d] for every rank d (this rank's token block inside rank d's output tensor): the
- * all-gather fused into the reduction.  Callers order the two kernels across ranks with
- * stream-ordered barriers; neither kernel waits on another GPU.
- */
-SFB200_API int sfb200_reduce_allgather(const void* slots, int tp, int rows, int cols,
-                                       void* const* peer_out_blocks, int dtype, const void* bias, void* stream);
-/* Same, for an output tensor that also has a switch-replicated (NVLS) mapping: switch_out_block is this
- * rank's token block inside that mapping, and every 16-byte result is written with one multimem.st that
- * NVSwitch delivers to all ranks, so the finished block leaves this GPU once instead of tp - 1 times. */
-SFB200_API int sfb200_reduce_allgather_switch(const void* slots, int tp, int rows, int cols, void* switch_out_block,
-                                              int dtype, const void* bias, void* stream);
-
-/*
- * The exchange step in ONE launch per rank, through NVSwitch (no counterpart in the reference).  Every rank has
- * written its partial output into its own copy of a symmetric buffer that also has a switch-replicated
- * ("multicast") mapping.  The kernel waits until all ranks have (flag words in symmetric memory, bounded polls),
- * sums this rank's token block across ranks inside the switch (multimem.ld_reduce, fp32 accumulation), adds the
- * bias, rounds once, writes the finished block into every rank's output (multimem.st), and returns once every
- * rank has finished, so the caller's next kernel may overwrite the partial buffer.
- *   mc_partial_block  this rank's token block ([rows, cols]) inside the MULTICAST mapping of the partial buffer
- *   mc_out_block      the same block inside the multicast mapping of the output tensor
- *   peer_flags        HOST array of tp device pointers: every rank's flag array (sfb200_tp_flag_words() uint32,
- *                     zero before the first launch, symmetric memory, used by no one else)
- *   epoch             1, 2, 3, ...: one per launch on these flags, the same on every rank
+ * Second half, ONE launch per rank with the cross-GPU ordering inside the kernel: waits until every rank's GEMM has
+ * finished (flag words in symmetric memory, bounded polls), adds the first `rows` rows of the tp local receive slots
+ * slots[tp][slot_rows, cols] in fp32, adds the bias, rounds once, stores the finished block into every rank's
+ * output -- peer_out_blocks[d] = this rank's token block inside rank d's output tensor (plain 16-byte peer stores), or
+ * mc_out_block when the output has a switch-replicated mapping (one multimem.st) -- and returns once every rank has
+ * finished, so the next step may overwrite the slots.
+ *   peer_flags  HOST array of tp device pointers: every rank's flag array (sfb200_tp_flag_words() uint32, zero before
+ *               the first launch, symmetric memory, used by no one else)
+ *   epoch       1, 2, 3, ...: one per launch on these flags, the same on every rank
  * Every rank must make the same sequence of calls.  A peer that never arrives makes the wait give up after 2 s:
  * sfb200_device_status then reports (2 << 8) | phase and the output is not valid.
  */
+SFB200_API int sfb200_tp_reduce_slots(const void* slots, int slot_rows, int slots_f32, void* mc_out_block,
+                                      void* const* peer_out_blocks, int rows, int cols, int dtype, const void* bias,
+                                      void* const* peer_flags, int tp, int rank, unsigned epoch, void* stream);
+/*
+ * The same exchange pulled through NVSwitch instead: every rank has written its partial output (sfb200_sparse_gemm or
+ * sfb200_sparse_gemm_f32out) into its own copy of a symmetric buffer that has a switch-replicated ("multicast")
+ * mapping; this rank's token block is summed across ranks inside the switch (multimem.ld_reduce) and the finished
+ * block written to every rank (multimem.st).  Same flags / epoch protocol.
+ *   mc_partial_block  this rank's token block ([rows, cols]) inside the MULTICAST mapping of the partial buffer;
+ *                     partial_f32 = 1: FLOAT partials, summed in fp32, output rounded once; partial_f32 = 0: 16-bit
+ *                     partials (half the bytes; every rank's partial carries its own 16-bit rounding)
+ *   mc_out_block      the same block inside the multicast mapping of the output tensor
+ */
 SFB200_API int sfb200_tp_allreduce_switch(const void* mc_partial_block, void* mc_out_block, int rows, int cols,
-                                          int dtype, const void* bias, void* const* peer_flags, int tp, int rank,
-                                          unsigned epoch, void* stream);
-/* Same protocol, no reduction: local_block ([rows, cols] 16-bit, LOCAL memory) is copied into mc_dst_block on every
- * rank (an all-gather of one block per rank, e.g. of the activations each rank uploaded). */
-SFB200_API int sfb200_tp_allgather_switch(const void* local_block, void* mc_dst_block, int rows, int cols,
-                                          void* const* peer_flags, int tp, int rank, unsigned epoch, void* stream);
+                                          int dtype, int partial_f32, const void* bias, void* const* peer_flags,
+                                          int tp, int rank, unsigned epoch, void* stream);
+/* Same protocol, no reduction: local_block ([rows, cols] 16-bit, LOCAL memory) is copied into every rank's buffer:
+ * mc_dst_block (multimem.st) when non-NULL, else peer_dst_blocks[d] (peer stores).  An all-gather of one block per
+ * rank, e.g. of the activations each rank uploaded. */
+SFB200_API int sfb200_tp_allgather(const void* local_block, void* mc_dst_block, void* const* peer_dst_blocks, int rows,
+                                   int cols, void* const* peer_flags, int tp, int rank, unsigned epoch, void* stream);
 SFB200_API int sfb200_tp_flag_words(void);
-
 /*
  * Gated FFN forward for callers that cannot allocate device memory (no counterpart in the
  * reference).  Same computation and bits as sfb200_ffn_forward, but the M x I hidden tensor lives
@@ -270,6 +279,11 @@ SFB200_API int sfb200_blob_read_header(const void* header_host, size_t available
  * with that many tokens; 3032/3064/3128 and 4032/4064/4128 = split-K cluster kernel with 2 or 4
  * K slices and a 32/64/128-token tile.  No counterpart upstream. */
 SFB200_API int sfb200_debug_force_token_tile(int bn);
+
+/* Tuning hooks of the prefill kernel's tile order (process-wide; no counterpart upstream): l2_band_mb > 0 sets
+ * the budget, in MB, of the band of the operand that is kept L2-resident (default 40); force_order picks that
+ * operand: -1 automatic (the smaller of activations and compressed weight), 0 activations, 1 weights. */
+SFB200_API int sfb200_debug_pair_tuning(int l2_band_mb, int force_order);
 
 /* The variant the library picks on its own for Y[M, N] = X[M, K] . W^T (swiglu = 1: the fused gate|up GEMM,
  * N = 2 * I rows) on a GPU with num_sms SMs, in the numbering above; 0 for a non-positive size.  Host-only. */

@@ -72,11 +72,11 @@ def lib() -> C.CDLL:
     L.sfb200_silu_mul.argtypes = [vp, i, vp, i, vp, i, i, i, i, vp]
     L.sfb200_ffn_forward.argtypes = [C.POINTER(FFNWeights), vp, i, vp, vp, i, i, vp]
     L.sfb200_ffn_forward_host.argtypes = [C.POINTER(FFNWeights), vp, vp, i, vp]
-    L.sfb200_sparse_gemm_scatter.argtypes = [vp, i, vp, vp, C.POINTER(vp), i, i, i, i, i, i, vp]
-    L.sfb200_reduce_allgather.argtypes = [vp, i, i, i, C.POINTER(vp), i, vp, vp]
-    L.sfb200_reduce_allgather_switch.argtypes = [vp, i, i, i, vp, i, vp, vp]
-    L.sfb200_tp_allreduce_switch.argtypes = [vp, vp, i, i, i, vp, C.POINTER(vp), i, i, C.c_uint, vp]
-    L.sfb200_tp_allgather_switch.argtypes = [vp, vp, i, i, C.POINTER(vp), i, i, C.c_uint, vp]
+    L.sfb200_sparse_gemm_scatter.argtypes = [vp, i, vp, vp, C.POINTER(vp), i, i, i, i, i, i, i, vp]
+    L.sfb200_tp_reduce_slots.argtypes = [vp, i, i, vp, C.POINTER(vp), i, i, i, vp, C.POINTER(vp), i, i, C.c_uint, vp]
+    L.sfb200_tp_allgather.argtypes = [vp, vp, C.POINTER(vp), i, i, C.POINTER(vp), i, i, C.c_uint, vp]
+    L.sfb200_tp_allreduce_switch.argtypes = [vp, vp, i, i, i, i, vp, C.POINTER(vp), i, i, C.c_uint, vp]
+    L.sfb200_sparse_gemm_f32out.argtypes = [vp, i, vp, vp, vp, i, i, i, i, i, vp, i, vp]
     L.sfb200_ffn_forward_noalloc.argtypes = [C.POINTER(FFNWeights), vp, i, vp, i, i, vp]
     L.sfb200_noalloc_device_status.argtypes = [C.POINTER(C.c_int)]
     L.sfb200_debug_wait_timeout.argtypes = [C.c_uint, i, i, vp]
@@ -101,6 +101,7 @@ def lib() -> C.CDLL:
     L.sf_get_counters.argtypes = [C.c_char_p, C.POINTER(C.c_int64), C.c_int32]
     L.sfb200_debug_force_token_tile.argtypes = [i]
     L.sfb200_debug_plan_gemm.argtypes = [i, i, i, i, i]
+    L.sfb200_debug_pair_tuning.argtypes = [i, i]
     L.sfb200_debug_host_pipeline.argtypes = [i, i]
     L.sfb200_debug_host_chunk_plan.argtypes = [i, i, i, C.POINTER(C.c_int)]
     L.sfb200_blob_bytes.restype = sz

@@ -343,17 +343,19 @@ int sfb200_ffn_forward_host(const sfb200_ffn_weights* w, const void* x_host, voi
 }
 
 int sfb200_sparse_gemm_scatter(const void* x, int ldx, const void* values, const void* meta,
-                               void* const* peer_slots, int tp, int tok_per_owner, int M, int N, int K, int dtype,
-                               void* stream) {
+                               void* const* peer_slots, int tp, int tok_per_owner, int slots_f32, int M, int N, int K,
+                               int dtype, void* stream) {
   int err = kOk;
   DeviceState* s = device_state(&err);
   if (!s) return err;
   if (!x || !values || !meta || !peer_slots) return kErrInvalid;
   if (dtype != kF16 && dtype != kBF16) return kErrInvalid;
+  Range r("sfb200.down_gemm_scatter");
   SparseGemmArgs a{};
   a.x = x;
   a.values = values;
   a.meta = meta;
+  a.y = peer_slots[0];      // unused by the kernel when peer_y is set; kept non-null for the launch checks
   a.status = s->status;
   a.m_tok = M;
   a.n_out = N;
@@ -364,48 +366,74 @@ int sfb200_sparse_gemm_scatter(const void* x, int ldx, const void* values, const
   a.epi = kEpiStore;
   a.act = kActNone;
   a.num_sms = s->num_sms;
-  Range r("sfb200.down_gemm_scatter");
-  return launch_sparse_gemm_pair_scatter(a, peer_slots, tp, tok_per_owner, static_cast<cudaStream_t>(stream));
+  a.force_bn = s->force_bn;
+  a.out_f32 = slots_f32 ? 1 : 0;
+  a.peer_y = peer_slots;
+  a.tp = tp;
+  a.tok_per_owner = tok_per_owner;
+  if (a.force_bn < 1000 || (a.force_bn >= 3000 && a.force_bn < 5000)) a.force_bn = pick_pair_variant(N, M, K, s->num_sms);
+  return launch_sparse_gemm_pair(a, static_cast<cudaStream_t>(stream));
 }
 
-int sfb200_reduce_allgather(const void* slots, int tp, int rows, int cols, void* const* peer_out_blocks, int dtype,
-                            const void* bias, void* stream) {
+int sfb200_sparse_gemm_f32out(const void* x, int ldx, const void* values, const void* meta, float* y, int ldy, int M,
+                              int N, int K, int dtype, const void* bias, int act, void* stream) {
   int err = kOk;
-  if (!device_state(&err)) return err;
-  if (!peer_out_blocks) return kErrInvalid;
-  Range r("sfb200.reduce_allgather");
-  return launch_reduce_allgather(slots, tp, rows, cols, peer_out_blocks, nullptr, dtype, bias,
-                                 static_cast<cudaStream_t>(stream));
-}
-
-int sfb200_reduce_allgather_switch(const void* slots, int tp, int rows, int cols, void* switch_out_block, int dtype,
-                                   const void* bias, void* stream) {
-  int err = kOk;
-  if (!device_state(&err)) return err;
-  if (!switch_out_block) return kErrInvalid;
-  return launch_reduce_allgather(slots, tp, rows, cols, nullptr, switch_out_block, dtype, bias,
-                                 static_cast<cudaStream_t>(stream));
+  DeviceState* s = device_state(&err);
+  if (!s) return err;
+  if (!x || !values || !meta || !y) return kErrInvalid;
+  if (dtype != kF16 && dtype != kBF16) return kErrInvalid;
+  Range r("sfb200.sparse_gemm_f32out");
+  SparseGemmArgs a{};
+  a.x = x;
+  a.values = values;
+  a.meta = meta;
+  a.y = y;
+  a.bias = bias;
+  a.status = s->status;
+  a.m_tok = M;
+  a.n_out = N;
+  a.K = K;
+  a.ldx = ldx;
+  a.ldy = ldy;
+  a.fmt = dtype;
+  a.epi = kEpiStore;
+  a.act = act;
+  a.num_sms = s->num_sms;
+  a.force_bn = s->force_bn;
+  a.out_f32 = 1;
+  return launch_sparse_gemm(a, static_cast<cudaStream_t>(stream));
 }
 
 int sfb200_tp_allreduce_switch(const void* mc_partial_block, void* mc_out_block, int rows, int cols, int dtype,
-                               const void* bias, void* const* peer_flags, int tp, int rank, unsigned epoch,
-                               void* stream) {
+                               int partial_f32, const void* bias, void* const* peer_flags, int tp, int rank,
+                               unsigned epoch, void* stream) {
   int err = kOk;
   DeviceState* s = device_state(&err);
   if (!s) return err;
   Range r("sfb200.tp_allreduce_switch");
-  return launch_switch_exchange(true, mc_partial_block, mc_out_block, rows, cols, dtype, bias, peer_flags, tp, rank,
-                                epoch, s->status, static_cast<cudaStream_t>(stream));
+  return launch_exchange(partial_f32 ? 2 : 1, mc_partial_block, mc_out_block, nullptr, rows, cols, rows, partial_f32, dtype,
+                         bias, peer_flags, tp, rank, epoch, s->status, static_cast<cudaStream_t>(stream));
 }
 
-int sfb200_tp_allgather_switch(const void* local_block, void* mc_dst_block, int rows, int cols, void* const* peer_flags,
-                               int tp, int rank, unsigned epoch, void* stream) {
+int sfb200_tp_allgather(const void* local_block, void* mc_dst_block, void* const* peer_dst_blocks, int rows, int cols,
+                        void* const* peer_flags, int tp, int rank, unsigned epoch, void* stream) {
   int err = kOk;
   DeviceState* s = device_state(&err);
   if (!s) return err;
-  Range r("sfb200.tp_allgather_switch");
-  return launch_switch_exchange(false, local_block, mc_dst_block, rows, cols, kBF16, nullptr, peer_flags, tp, rank,
-                                epoch, s->status, static_cast<cudaStream_t>(stream));
+  Range r("sfb200.tp_allgather");
+  return launch_exchange(0, local_block, mc_dst_block, peer_dst_blocks, rows, cols, rows, 0, kBF16, nullptr, peer_flags, tp,
+                         rank, epoch, s->status, static_cast<cudaStream_t>(stream));
+}
+
+int sfb200_tp_reduce_slots(const void* slots, int slot_rows, int slots_f32, void* mc_out_block, void* const* peer_out_blocks,
+                           int rows, int cols, int dtype, const void* bias, void* const* peer_flags, int tp, int rank,
+                           unsigned epoch, void* stream) {
+  int err = kOk;
+  DeviceState* s = device_state(&err);
+  if (!s) return err;
+  Range r("sfb200.tp_reduce_slots");
+  return launch_exchange(3, slots, mc_out_block, peer_out_blocks, rows, cols, slot_rows, slots_f32, dtype, bias, peer_flags,
+                         tp, rank, epoch, s->status, static_cast<cudaStream_t>(stream));
 }
 
 int sfb200_tp_flag_words(void) { return kSwitchFlagWords; }
@@ -416,6 +444,12 @@ SFB200_API int sfb200_debug_force_token_tile(int bn) {
   DeviceState* s = device_state(&err);
   if (!s) return err;
   s->force_bn = bn;
+  return kOk;
+}
+
+SFB200_API int sfb200_debug_pair_tuning(int l2_band_mb, int force_order) {
+  if (force_order < -1 || force_order > 1) return kErrInvalid;
+  set_pair_tuning(l2_band_mb, force_order);
   return kOk;
 }
 

@@ -64,41 +64,42 @@ struct SparseGemmArgs {
   int act;
   int num_sms;
   int force_bn;           // 0 = choose by token count
+  int out_f32;            // 1: y is float [m_tok, ldy], results stored unrounded (kEpiStore, CTA-pair kernel only)
+  // Row-parallel GEMM of a tensor-parallel FFN with the reduce-scatter fused into the epilogue (CTA-pair kernel,
+  // kEpiStore): token block o (tok_per_owner tokens, a multiple of 16) of this rank's partial output is stored to
+  // peer_y[o] -- rank o's receive slot for this rank, [tok_per_owner, ldy], 16-bit or float per out_f32 -- instead of y.
+  // peer_y: HOST array of tp device pointers (peer-mapped memory), or null.
+  void* const* peer_y;
+  int tp;
+  int tok_per_owner;
 };
 int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream);
 // CTA-pair (cta_group::2) variant, 256-row x 256-token tiles; chosen by launch_sparse_gemm for
 // m_tok >= kPairMinTokens.  force_bn 1192..1256 (256-row tiles) or 2192..2240 (512-row tiles) picks a variant.
 int launch_sparse_gemm_pair(const SparseGemmArgs& a, cudaStream_t stream);
 constexpr int kPairMinTokens = 1024;
+// Tuning hooks of the CTA-pair kernel's tile order: budget (MB) of the L2-resident operand's band (<= 0: keep),
+// and which operand is resident (-1 automatic, 0 activations, 1 weights).  Process-wide.
+void set_pair_tuning(int l2_band_mb, int force_order);
 // Variant the CTA-pair launcher picks on its own (1192..1256 or 2192..2240).
 int pick_pair_variant(int n_out, int m_tok, int K, int num_sms);
 // The kernel variant launch_sparse_gemm runs for a shape when nothing is forced, in the numbering of
 // SparseGemmArgs::force_bn: 8 decode kernel; 32..256 single-CTA kernel with that token tile; 1192..1256 / 2192..2240
 // CTA-pair kernel; 3000 + tile / 4000 + tile split-K cluster kernel with 2 / 4 K slices.  Host-only.
 int plan_sparse_gemm(int m_tok, int n_out, int K, int epi, int num_sms);
-// Row-parallel GEMM of a tensor-parallel FFN with the reduce-scatter fused into the epilogue:
-// token block o of this rank's partial output is stored into peer_slots[o] (rank o's receive slot
-// for this rank, [tok_per_owner, n_out], peer-mapped memory).
-int launch_sparse_gemm_pair_scatter(const SparseGemmArgs& a, void* const* peer_slots, int tp, int tok_per_owner,
-                                    cudaStream_t stream);
-// out_block = sum over tp receive slots (fp32), written to every rank's output at this rank's token
-// block (all-gather fused into the reduction).  slots: [tp][rows, cols] contiguous, local.
-// switch_out_block != null: this rank's block inside the switch-replicated mapping of the output (one multimem
-// store reaches every rank) and peer_out_blocks is ignored.
-int launch_reduce_allgather(const void* slots, int tp, int rows, int cols, void* const* peer_out_blocks,
-                            void* switch_out_block, int fmt, const void* bias, cudaStream_t stream);
-
-// The exchange step in one launch, through the switch-replicated (multicast) mappings of symmetric buffers.
-// reduce = true:  src = this rank's token block inside the MULTICAST mapping of the partial-sum buffer; the block is
-//                 summed across ranks in the switch (fp32 accumulation), bias added, rounded once and written to
-//                 mc_dst, this rank's block inside the multicast mapping of the output (every rank receives it).
-// reduce = false: src = LOCAL data ([rows, cols]), copied to mc_dst on every rank (all-gather of one block per rank).
+// The exchange step (reduction + all-gather) of the row-parallel GEMM in one launch per rank, cross-GPU ordering
+// included.  mode 3: src = LOCAL receive slots [tp][slot_rows, cols] (float or 16-bit per slots_f32) that the ranks' GEMM
+// epilogues filled; the first `rows` rows of every slot are summed in fp32, bias added, rounded once and stored into
+// every rank's output block (peer_dst[d], plain peer stores; or mc_dst, one multimem store).  mode 1 / 2: src = this
+// rank's block inside the MULTICAST mapping of a symmetric buffer of 16-bit / float partial sums, summed inside
+// NVSwitch; needs mc_dst.  mode 0: src = local 16-bit block, copied to every rank (all-gather).
 // peer_flags: HOST array of tp device pointers, every rank's flag array of kSwitchFlagWords uint32 (zeroed once,
-// symmetric memory); epoch: 1, 2, 3, ... one per launch, the same on every rank.  Bounded waits; on a timeout the
-// status word receives (2 << 8) | phase.
+// symmetric memory); epoch: 1, 2, 3, ... one per launch on that flag array, the same on every rank.  Bounded waits; on
+// a timeout the status word receives (2 << 8) | phase.
 constexpr int kSwitchFlagWords = 2 * 148 * 8;
-int launch_switch_exchange(bool reduce, const void* src, void* mc_dst, int rows, int cols, int fmt, const void* bias,
-                           void* const* peer_flags, int tp, int rank, unsigned epoch, int* status, cudaStream_t stream);
+int launch_exchange(int mode, const void* src, void* mc_dst, void* const* peer_dst, int rows, int cols, int slot_rows,
+                    int slots_f32, int fmt, const void* bias, void* const* peer_flags, int tp, int rank, unsigned epoch,
+                    int* status, cudaStream_t stream);
 
 // Split-K variant of the single-CTA kernel: a cluster of `split` (2 or 4) CTAs shares one output tile,
 // each streaming a slice of K; partial tiles are reduced through distributed shared memory.  Chosen by

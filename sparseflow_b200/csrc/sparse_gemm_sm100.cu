@@ -436,9 +436,17 @@ int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream) {
     return kErrInvalid;
   if (a.epi == kEpiSwiGLU && (a.n_out % 32 != 0 || (a.n_out / 2) % 8 != 0)) return kErrInvalid;
   SparseGemmArgs b = a;
+  if (a.out_f32) {
+    // fp32 output exists in the CTA-pair kernel's epilogue only
+    if (a.epi != kEpiStore) return kErrInvalid;
+    if (b.force_bn < 1000 || (b.force_bn >= 3000 && b.force_bn < 5000))
+      b.force_bn = pick_pair_variant(a.n_out, a.m_tok, a.K, a.num_sms);
+    return launch_sparse_gemm_pair(b, stream);
+  }
   if (b.force_bn == 0) b.force_bn = plan_sparse_gemm(a.m_tok, a.n_out, a.K, a.epi, a.num_sms);
   const int v = b.force_bn;
   if (v == 8) return launch_sparse_gemm_small_m(b, stream);
+  if (v >= 5000) return launch_sparse_gemm_pair(b, stream);
   if (v >= 3000) return launch_sparse_gemm_splitk(b, v >= 4000 ? 4 : 2, stream);
   if (v >= 1000) return launch_sparse_gemm_pair(b, stream);
   return a.epi == kEpiSwiGLU ? dispatch_bn<kEpiSwiGLU>(b, stream) : dispatch_bn<kEpiStore>(b, stream);

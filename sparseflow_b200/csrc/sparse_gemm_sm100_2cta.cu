@@ -72,14 +72,6 @@ __device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t dst, const CUtens
       "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(leader_bar), "l"(policy)
       : "memory");
 }
-__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* m, uint32_t src, int x, int y,
-                                                  uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"(
-          reinterpret_cast<uint64_t>(m)),
-      "r"(src), "r"(x), "r"(y), "l"(policy)
-      : "memory");
-}
 __device__ __forceinline__ void tma_load_1d_pair(uint32_t dst, const CUtensorMap* m, int x,
                                                  uint32_t leader_bar) {
   asm volatile(
@@ -132,42 +124,72 @@ struct PairParams {
   int num_m_blks, num_n_blks;   // (256*RS)-row / BN-token tiles
   int k_tiles128;
   int fmt, act;
-  int tok_per_owner;   // scatter epilogue: tokens owned by each rank (0 = plain output)
-  int band;            // token tiles per L2 band (see tile_coords)
+  int tok_per_owner;   // > 0: token block o (tok_per_owner tokens) is stored to peer_y[o] instead of y (reduce-scatter
+                       // fused into the epilogue: peer_y[o] = rank o's receive slot for this rank's partial sums)
+  void* peer_y[8];
+  int band;            // tiles of the RESIDENT operand per L2 band (see tile_coords)
+  int order;           // 0: activations resident (bands of token tiles); 1: weights resident (bands of row tiles)
+  int out_f32;         // store epilogue: y is float [m_tok, ldy] and the fp32 results are stored unrounded
 };
 
-// Tile order.  Tiles are walked band by band: a band is `band` consecutive token tiles, and inside a
-// band the row tile is the slow index.  The SM pairs working at the same time therefore share one or
-// two weight tiles and one band of activations; the band is sized so that its activations stay in
-// L2 while every row tile passes over them.  Without bands, a token operand larger than L2 (16384
-// tokens x 4096, 8192 x 8192) is re-read from HBM once per row tile and the GEMM becomes HBM-bound.
+// Tile order.  The SM pairs run in lockstep along K, so data shared by the tiles of one pass over the SMs
+// ("wave") is fetched from HBM once; what decides the L2 hit rate is whether the operand that the NEXT
+// wave needs again is still there.  One operand is therefore kept resident (loaded with an evict-last
+// hint) and the other is streamed: the resident operand is cut into bands of about 40 MB, and inside a band
+// the tiles of the streamed operand are the slow index, so that every wave touches the whole band of the
+// resident operand and only a few tiles of the streamed one.
+//   order 0: activations resident (bands of token tiles, row tile slow inside a band): gate|up-like shapes,
+//            where the activations are the smaller operand;
+//   order 1: weights resident (bands of row tiles, token tile slow inside a band): down-projection-like
+//            shapes (long K, few rows), where hidden[M, I] is larger than the compressed weight.  (Measured on
+//            4096 x 11008 at 4096 tokens with order 0: 72 % L2 hit rate, 325 MB read from HBM for 140 MB of
+//            operands; the gate|up shape, whose activations fit, runs at 94 %.)
 __device__ __forceinline__ void tile_coords(int tile, const PairParams& p, int& m_blk, int& n_blk) {
-  const int per_band = p.num_m_blks * p.band;
-  const int b = tile / per_band;
-  const int r = tile - b * per_band;
-  const int left = p.num_n_blks - b * p.band;
-  const int width = left < p.band ? left : p.band;
-  m_blk = r / width;
-  n_blk = b * p.band + (r - m_blk * width);
+  if (p.order == 0) {
+    const int per_band = p.num_m_blks * p.band;
+    const int b = tile / per_band;
+    const int r = tile - b * per_band;
+    const int left = p.num_n_blks - b * p.band;
+    const int width = left < p.band ? left : p.band;
+    m_blk = r / width;
+    n_blk = b * p.band + (r - m_blk * width);
+  } else {
+    const int per_band = p.num_n_blks * p.band;
+    const int b = tile / per_band;
+    const int r = tile - b * per_band;
+    const int left = p.num_m_blks - b * p.band;
+    const int height = left < p.band ? left : p.band;
+    n_blk = r / height;
+    m_blk = b * p.band + (r - n_blk * height);
+  }
 }
 
-// Token tiles per band: activations of a band (tokens x K x 2 bytes) within ~40 MB of the 126 MB L2.
-inline int pick_band(int bn, int K, int num_n_blks) {
-  const long per_blk = static_cast<long>(bn) * K * 2;
-  long band = (40l << 20) / (per_blk > 0 ? per_blk : 1);
+int g_force_order = -1;  // tuning hook: -1 automatic, 0 / 1 force the tile order
+int g_l2_band_mb = 40;   // budget of the resident operand's band (tuning hook: set_l2_band_mb)
+
+// Tiles of the resident operand per band: `per_blk` bytes each, `count` of them in all.
+inline int pick_band(long per_blk, int count) {
+  long band = (static_cast<long>(g_l2_band_mb) << 20) / (per_blk > 0 ? per_blk : 1);
   if (band < 1) band = 1;
-  if (band >= num_n_blks) return num_n_blks;
-  // equal-width bands: avoid a narrow last band
-  const long nb = (num_n_blks + band - 1) / band;
-  band = (num_n_blks + nb - 1) / nb;
+  if (band >= count) return count;
+  // equal bands: avoid a narrow last band
+  const long nb = (count + band - 1) / band;
+  band = (count + nb - 1) / nb;
   return static_cast<int>(band);
 }
 
-// Output tensor maps of the scatter epilogue: one per destination rank (its receive slot for this
-// rank's partial sums, mapped into this GPU's address space).
-struct ScatterMaps {
-  CUtensorMap m[8];
-};
+// Which operand stays resident, and the band size, for a rows x K weight against m_tok tokens.
+inline void pick_order(int n_out, int m_tok, int K, int rows_tile, int bn, int num_m_blks, int num_n_blks,
+                       PairParams& p) {
+  const double w_bytes = static_cast<double>(n_out) * K * 1.125, x_bytes = static_cast<double>(m_tok) * K * 2.0;
+  if (w_bytes < x_bytes) {
+    p.order = 1;
+    p.band = pick_band(static_cast<long>(rows_tile * 1.125 * K), num_m_blks);
+  } else {
+    p.order = 0;
+    p.band = pick_band(static_cast<long>(bn) * K * 2, num_n_blks);
+  }
+}
 
 template <int BN_, int BK_, int STAGES_, int RS_, int EPI_>
 struct PairCfg {
@@ -201,24 +223,26 @@ struct PairCfg {
   static constexpr int OFF_A = 0;
   static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
   static constexpr int OFF_E = OFF_B + STAGES * B_BYTES;
-  // per-warp output staging for the register-drain epilogue (RS = 1): 2 buffers of 16 tokens x
+  // per-warp output staging for the register-drain epilogue: 2 buffers of 16 tokens x
   // 32 rows (or 16 features for SiLU.mul) of 16-bit values
   static constexpr int D_ROW_BYTES = (EPI == kEpiSwiGLU) ? 32 : 64;
   static constexpr int D_BUF_BYTES = 16 * D_ROW_BYTES;
   static constexpr int OFF_D = OFF_E + E_STAGES * E_BYTES;
-  static constexpr int D_BYTES = (RS == 1) ? 8 * 2 * D_BUF_BYTES : 0;
+  static constexpr int D_BYTES = 8 * 2 * D_BUF_BYTES;
   static constexpr int OFF_BAR = OFF_D + D_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
   static constexpr int EPI_WARPS = 8;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
-  // 8 epilogue warps = 4 lane quadrants x 2.  RS = 2: each takes one accumulator.  RS = 1: each
-  // loads 128 columns, the first [0, 128), the second [BN - 128, BN); the second one stores only
-  // what the first does not cover, i.e. it skips its first (256 - BN) / 16 chunks.
-  static constexpr int COLS_PER_WARP = (RS == 1) ? 128 : BN;
-  static constexpr int SKIP_CHUNKS = (RS == 1) ? (256 - BN) / 16 : 0;
+  // 8 epilogue warps = 4 lane quadrants x 2.  The accumulator is drained through registers in windows
+  // of 128 columns, [0, 128) and [BN - 128, BN); the second window stores only what the first does not
+  // cover, i.e. it skips its first (256 - BN) / 16 chunks.  RS = 1: the two warps of a quadrant take one
+  // window each.  RS = 2: each warp takes one accumulator and drains both windows in turn.
+  static constexpr int COLS_PER_WARP = 128;
+  static constexpr int SKIP_CHUNKS = (256 - BN) / 16;
+  static constexpr int PASSES = RS;
   static_assert(RS == 1 || RS == 2, "RS");
   static_assert(BK == 128 || STAGES % 2 == 0, "BK = 64 needs an even stage count");
-  static_assert(BN % 16 == 0 && BN <= 256 && (RS == 2 || BN >= 128), "BN");
+  static_assert(BN % 16 == 0 && BN <= 256 && BN >= 128, "BN");
   static_assert(HALF_N % 8 == 0, "token half must be whole swizzle atoms");
   static_assert(COLS_PER_WARP % 16 == 0, "epilogue chunking");
   static_assert(TMEM_USED <= 512, "tmem");
@@ -233,28 +257,11 @@ __device__ __forceinline__ float act_fn(float v, int act) {
     default: return v;
   }
 }
-__device__ __forceinline__ uint16_t to16(float v, int fmt) {
-  if (fmt == 1) return __bfloat16_as_ushort(__float2bfloat16_rn(v));
-  return __half_as_ushort(__float2half_rn(v));
-}
 __device__ __forceinline__ float bias_at(const void* bias, int o, int fmt) {
   const uint16_t b = static_cast<const uint16_t*>(bias)[o];
   if (fmt == 1) return __uint_as_float(static_cast<uint32_t>(b) << 16);
   return __half2float(__ushort_as_half(b));
 }
-// 32 lanes x 16 columns of fp32
-__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-
-
 // 16 lanes x 128 columns: thread l gets, for repetition n (8 columns each), r[4n], r[4n+1] =
 // (lane l/4, columns 8n + 2(l%4), +1) and r[4n+2], r[4n+3] = (lane l/4 + 8, same columns): the
 // accumulator-fragment layout of warp-level MMA, which stmatrix can transpose.
@@ -263,6 +270,24 @@ __device__ __forceinline__ void tmem_ld_16x256b_x16(uint32_t taddr, uint32_t (&r
       "tcgen05.ld.sync.aligned.16x256b.x16.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+      : "r"(taddr)
+      : "memory");
+}
+// Same layout, 16 columns (two repetitions): 8 registers.
+__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+// 32 lanes x 16 columns of fp32: thread i = lane base + i, one register per column
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }
@@ -285,37 +310,9 @@ __device__ __forceinline__ float silu_mul(uint32_t g, uint32_t u) {
   return (gf * __fdividef(1.f, 1.f + __expf(-gf))) * __uint_as_float(u);
 }
 
-// One 16-column chunk of this lane's row: tokens tok0 .. tok0+15.
-template <int EPI>
-__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[16], const PairParams& p,
-                                               uint16_t* ycol, bool col_ok, int tok0, float bias_v,
-                                               bool upper) {
-  if (EPI == kEpiStore) {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float v = act_fn(__uint_as_float(r[j]) + bias_v, p.act);
-      if (col_ok && tok0 + j < p.m_tok) ycol[static_cast<size_t>(tok0 + j) * p.ldy] = to16(v, p.fmt);
-    }
-  } else {
-    // lanes 0..15 hold gate(f), lanes 16..31 up(f); per token pair the lower half-warp produces
-    // token j, the upper half-warp token j+1.
-#pragma unroll
-    for (int j = 0; j < 16; j += 2) {
-      const uint32_t send = upper ? r[j] : r[j + 1];
-      const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 16);
-      const float g = __uint_as_float(upper ? recv : r[j]);
-      const float u = __uint_as_float(upper ? r[j + 1] : recv);
-      const float sg = __fdividef(1.f, 1.f + __expf(-g));
-      const int t = tok0 + j + (upper ? 1 : 0);
-      if (col_ok && t < p.m_tok) ycol[static_cast<size_t>(t) * p.ldy] = to16((g * sg) * u, p.fmt);
-    }
-  }
-}
-
-template <class C, bool SCATTER>
+template <class C>
 __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const CUtensorMap& tmB,
-                                                 const CUtensorMap& tmE, const CUtensorMap& tmD,
-                                                 const ScatterMaps* tmS, const PairParams& p) {
+                                                 const CUtensorMap& tmE, const PairParams& p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -353,7 +350,6 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     tma_prefetch_desc(&tmE);
-    tma_prefetch_desc(&tmD);
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(tmem_slot), C::TMEM_COLS);
@@ -370,6 +366,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
     if (elect_one()) {
       const uint32_t leader_full0 = mapa_u32(bar_full, 0);
       const uint64_t pol_keep = l2_policy_evict_last();
+      const bool keep_x = p.order == 0;      // the resident operand is loaded evict-last, the streamed one plainly
       int s = 0, es = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -387,11 +384,14 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
           if (leader)   // bytes of BOTH CTAs land on this barrier
             mbar_arrive_expect_tx(bar_full + 8 * s,
                                   2 * (C::A_BYTES + C::B_BYTES + (load_e ? C::E_BYTES : 0)));
-          tma_load_2d_pair(sbase + C::OFF_A + s * C::A_BYTES, &tmA, kt * (C::BK / 2), row0, full);
+          if (keep_x) tma_load_2d_pair(sbase + C::OFF_A + s * C::A_BYTES, &tmA, kt * (C::BK / 2), row0, full);
+          else tma_load_2d_pair_hint(sbase + C::OFF_A + s * C::A_BYTES, &tmA, kt * (C::BK / 2), row0, full, pol_keep);
 #pragma unroll
-          for (int j = 0; j < C::B_SUBS; ++j)
-            tma_load_2d_pair_hint(sbase + C::OFF_B + s * C::B_BYTES + j * C::B_SUB_BYTES, &tmB,
-                                  kt * C::BK + j * 64, tok0, full, pol_keep);
+          for (int j = 0; j < C::B_SUBS; ++j) {
+            const uint32_t dst = sbase + C::OFF_B + s * C::B_BYTES + j * C::B_SUB_BYTES;
+            if (keep_x) tma_load_2d_pair_hint(dst, &tmB, kt * C::BK + j * 64, tok0, full, pol_keep);
+            else tma_load_2d_pair(dst, &tmB, kt * C::BK + j * 64, tok0, full);
+          }
           if (load_e) {
             const int kt128 = (C::BK == 128) ? kt : (kt >> 1);
 #pragma unroll
@@ -468,8 +468,6 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
     const uint32_t leader_acce0 = mapa_u32(bar_acce, 0);
     const uint64_t pol_stream = l2_policy_evict_first();
     bool ok = true;
-    constexpr int NCH = C::COLS_PER_WARP / 16;
-    const bool upper = lane >= 16;
     uint32_t it = 0;
     for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++it) {
       int m_blk, n_blk;
@@ -486,37 +484,124 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
       const int row_w = m_blk * C::ROWS_TILE + static_cast<int>(rank) * C::ROWS_CTA + acc * 128 + q * 32;
       const int tok_w = n_blk * C::BN + col0;
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * C::ACC_COLS + acc * C::BN + col0;
-      uint16_t* ycol;
-      bool col_ok;
-      float bias_v = 0.f;
-      if (C::EPI == kEpiStore) {
-        const int row = row_w + lane;
-        col_ok = row < p.n_out;
-        ycol = static_cast<uint16_t*>(p.y) + row;
-        if (p.bias != nullptr && col_ok) bias_v = bias_at(p.bias, row, p.fmt);
-      } else {
-        const int f = row_w / 2 + (lane & 15);
-        col_ok = f < p.n_out / 2;
-        ycol = static_cast<uint16_t*>(p.y) + f;
-      }
-      if constexpr (C::RS == 1) {
-        // Register drain: both 16-lane halves of this warp's quadrant, all its columns, in the
-        // MMA-fragment layout; one wait; accumulator handed back; everything else afterwards.
-        constexpr int NCOL = C::COLS_PER_WARP;          // 128 (or 64)
-        static_assert(NCOL == 128, "register-drain epilogue is written for 128 columns per warp");
-        uint32_t va[64], vb[64];
-        tmem_ld_16x256b_x16(t_acc, va);                                          // lanes q*32 + 0..15
-        tmem_ld_16x256b_x16(t_acc + (static_cast<uint32_t>(16) << 16), vb);      // lanes q*32 + 16..31
-        tmem_ld_wait();
+      // Two forms of the drain.  The epilogue's code is executed once per tile by 8 warps that are out of step with
+      // one another, so a fully unrolled drain (thousands of instructions: 128 accumulator registers converted and
+      // stored one by one) runs out of the instruction cache: measured ~17 stall cycles per issued instruction and
+      // 15 - 25 us of epilogue per tile, which bounds every tile whose K loop is shorter than that.  Where the tile has
+      // TWO accumulator sets the drain is therefore a ROLLED loop over 16-column chunks (load, wait, convert, store;
+      // ~150 instructions), and the accumulator is handed back after the last chunk: the MMA stream is already filling
+      // the other set.  With ONE accumulator set the accumulator has to go back as early as possible, so it is read
+      // into registers in one piece (unrolled) and handed back before conversion and stores.
+      constexpr bool kRolled = C::ACC_BUFS == 2;
+      const int out_cols = (C::EPI == kEpiSwiGLU) ? p.n_out / 2 : p.n_out;
+      const int g = lane >> 2;
+      const uint32_t stage0 = sbase + C::OFF_D + (warp - 2) * 2 * C::D_BUF_BYTES;
+      // stmatrix row address of this lane: matrix = lane / 8, row in matrix = lane % 8
+      const int mt = lane >> 3, rr = lane & 7;
+      const uint32_t st_off = static_cast<uint32_t>((rr + 8 * (mt >> 1)) * C::D_ROW_BYTES + 16 * (mt & 1));
+      const int out_x = (C::EPI == kEpiSwiGLU) ? row_w / 2 : row_w;   // first output column of this warp
+
+      // destination of the 16-token chunk that starts at token t0: the output tensor, or (row-parallel GEMM with the
+      // reduce-scatter fused in) the receive slot of the rank that owns these tokens -- stores over NVLink
+      auto chunk_dst = [&](int t0, int& tl) -> void* {
+        tl = t0;
+        if (C::EPI == kEpiStore && p.tok_per_owner > 0) {
+          const int owner = t0 / p.tok_per_owner;
+          tl = t0 - owner * p.tok_per_owner;
+          return p.peer_y[owner < 8 ? owner : 7];
+        }
+        return p.y;
+      };
+      // 16-bit output of one chunk whose fragment registers are a[0..8) (lanes 0-15 of the quadrant) and b[0..8)
+      // (lanes 16-31): transpose through the staging tile, then plain 16-byte stores.  (A TMA store per chunk queues
+      // behind the producer's loads in the copy engine and its completion, which the staging buffer's reuse has to
+      // wait for, takes longer than the chunk itself.)
+      auto store_chunk16 = [&](const uint32_t* a, const uint32_t* b, int c, int t0, float b0, float b1, float b2, float b3) {
+        const uint32_t stage = stage0 + (c & 1) * C::D_BUF_BYTES;
+        __syncwarp();                                 // every lane has read this buffer's previous contents
+        if (C::EPI == kEpiSwiGLU) {
+          // half 0 = 16 gate rows, half 1 = the 16 matching up rows: pairing is in-thread
+          stmatrix_x4_trans(stage + st_off, pack16(silu_mul(a[0], b[0]), silu_mul(a[1], b[1]), p.fmt),
+                            pack16(silu_mul(a[2], b[2]), silu_mul(a[3], b[3]), p.fmt),
+                            pack16(silu_mul(a[4], b[4]), silu_mul(a[5], b[5]), p.fmt),
+                            pack16(silu_mul(a[6], b[6]), silu_mul(a[7], b[7]), p.fmt));
+        } else {
+          auto f = [&](uint32_t v, float bias) { return act_fn(__uint_as_float(v) + bias, p.act); };
+          stmatrix_x4_trans(stage + st_off, pack16(f(a[0], b0), f(a[1], b0), p.fmt), pack16(f(a[2], b1), f(a[3], b1), p.fmt),
+                            pack16(f(a[4], b0), f(a[5], b0), p.fmt), pack16(f(a[6], b1), f(a[7], b1), p.fmt));
+          stmatrix_x4_trans(stage + st_off + 32, pack16(f(b[0], b2), f(b[1], b2), p.fmt),
+                            pack16(f(b[2], b3), f(b[3], b3), p.fmt), pack16(f(b[4], b2), f(b[5], b2), p.fmt),
+                            pack16(f(b[6], b3), f(b[7], b3), p.fmt));
+        }
+        int tl;
+        uint16_t* base = static_cast<uint16_t*>(chunk_dst(t0, tl));
+        __syncwarp();
+        constexpr int UNITS_PER_TOK = C::D_ROW_BYTES / 16;          // 4 (store) or 2 (SiLU.mul)
+#pragma unroll
+        for (int j = 0; j < UNITS_PER_TOK / 2; ++j) {
+          const int u = lane + 32 * j;
+          const int tk = u / UNITS_PER_TOK, part = u % UNITS_PER_TOK;
+          const int col = out_x + part * 8;
+          if (t0 + tk < p.m_tok && col < out_cols) {
+            uint4 v;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                         : "r"(stage + tk * C::D_ROW_BYTES + part * 16));
+            uint16_t* dst = base + static_cast<size_t>(tl + tk) * p.ldy + col;
+            asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(dst), "r"(v.x), "r"(v.y),
+                         "r"(v.z), "r"(v.w), "l"(pol_stream)
+                         : "memory");
+          }
+        }
+      };
+      // fp32 output of one chunk (partial sums that are added across ranks before they are rounded): the 32x32b load
+      // gives every thread ONE row and 16 consecutive tokens, so a warp's store of one token is 32 consecutive floats
+      // = 128 contiguous bytes: no transposition, full-size writes also when the destination is another GPU.
+      auto store_chunk32 = [&](const uint32_t* r, int t0, float bias_v, bool row_ok) {
+        int tl;
+        float* dst = static_cast<float*>(chunk_dst(t0, tl)) + static_cast<size_t>(tl) * p.ldy + row_w + lane;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (row_ok && t0 + j < p.m_tok) dst[static_cast<size_t>(j) * p.ldy] = act_fn(__uint_as_float(r[j]) + bias_v, p.act);
+      };
+      auto release_acc = [&]() {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_remote(leader_acce);
+      };
 
-        const int g = lane >> 2;
-        const uint32_t stage0 = sbase + C::OFF_D + (warp - 2) * 2 * C::D_BUF_BYTES;
-        // stmatrix row address of this lane: matrix = lane / 8, row in matrix = lane % 8
-        const int mt = lane >> 3, rr = lane & 7;
-        const uint32_t st_off = static_cast<uint32_t>((rr + 8 * (mt >> 1)) * C::D_ROW_BYTES + 16 * (mt & 1));
+      if (C::EPI == kEpiStore && p.out_f32) {
+        const bool row_ok = row_w + lane < p.n_out;
+        const float bias_v = (p.bias != nullptr && row_ok) ? bias_at(p.bias, row_w + lane, p.fmt) : 0.f;
+        if constexpr (kRolled) {
+          uint32_t r[16];
+#pragma unroll 1
+          for (int c = c_begin; c < 8; ++c) {
+            tmem_ld_32x32b_x16(t_acc + 16 * c, r);
+            tmem_ld_wait();
+            const int t0 = tok_w + c * 16;
+            if (t0 < p.m_tok) store_chunk32(r, t0, bias_v, row_ok);
+          }
+          release_acc();
+        } else {
+          uint32_t vr[128];
+#pragma unroll
+          for (int ps = 0; ps < C::PASSES; ++ps) {
+            const int win = (C::RS == 1) ? 0 : ps * (C::BN - 128);
+            const int cb = (C::RS == 1) ? c_begin : ps * C::SKIP_CHUNKS;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              tmem_ld_32x32(t_acc + win + 32 * k, reinterpret_cast<uint32_t(&)[32]>(vr[32 * k]));
+            tmem_ld_wait();
+            if (ps == C::PASSES - 1) release_acc();
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const int t0 = tok_w + win + c * 16;
+              if (c >= cb && t0 < p.m_tok) store_chunk32(&vr[16 * c], t0, bias_v, row_ok);
+            }
+          }
+        }
+      } else {
         float b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;   // bias of rows g, g+8, 16+g, 24+g
         if (C::EPI == kEpiStore && p.bias != nullptr) {
           if (row_w + g < p.n_out) b0 = bias_at(p.bias, row_w + g, p.fmt);
@@ -524,66 +609,36 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
           if (row_w + g + 16 < p.n_out) b2 = bias_at(p.bias, row_w + g + 16, p.fmt);
           if (row_w + g + 24 < p.n_out) b3 = bias_at(p.bias, row_w + g + 24, p.fmt);
         }
-        const int out_x = (C::EPI == kEpiSwiGLU) ? row_w / 2 : row_w;   // first output column of this warp
+        if constexpr (kRolled) {
+          uint32_t a[8], b[8];
+#pragma unroll 1
+          for (int c = c_begin; c < 8; ++c) {
+            tmem_ld_16x256b_x2(t_acc + 16 * c, a);                                          // lanes q*32 + 0..15
+            tmem_ld_16x256b_x2(t_acc + 16 * c + (static_cast<uint32_t>(16) << 16), b);      // lanes q*32 + 16..31
+            tmem_ld_wait();
+            store_chunk16(a, b, c, tok_w + c * 16, b0, b1, b2, b3);
+          }
+          release_acc();
+        } else {
+          // both 16-lane halves of this warp's quadrant, one window of 128 columns, in the MMA-fragment layout; one
+          // wait per window; the accumulator is handed back after the LAST window's loads have landed
+          uint32_t va[64], vb[64];
 #pragma unroll
-        for (int c = 0; c < NCOL / 16; ++c) {
-          if (c < c_begin) continue;                   // columns the other warp of this quadrant stores
-          const uint32_t stage = stage0 + (c & 1) * C::D_BUF_BYTES;
-          if (lane == 0) tma_store_wait_read<1>();     // the buffer's previous store has read it
-          __syncwarp();
-          const int o = 8 * c;                          // registers of this 16-column chunk
-          if (C::EPI == kEpiSwiGLU) {
-            // half 0 = 16 gate rows, half 1 = the 16 matching up rows: pairing is in-thread
-            const uint32_t h0 = pack16(silu_mul(va[o + 0], vb[o + 0]), silu_mul(va[o + 1], vb[o + 1]), p.fmt);
-            const uint32_t h1 = pack16(silu_mul(va[o + 2], vb[o + 2]), silu_mul(va[o + 3], vb[o + 3]), p.fmt);
-            const uint32_t h2 = pack16(silu_mul(va[o + 4], vb[o + 4]), silu_mul(va[o + 5], vb[o + 5]), p.fmt);
-            const uint32_t h3 = pack16(silu_mul(va[o + 6], vb[o + 6]), silu_mul(va[o + 7], vb[o + 7]), p.fmt);
-            stmatrix_x4_trans(stage + st_off, h0, h1, h2, h3);
-          } else {
-            auto f = [&](uint32_t v, float bias) { return act_fn(__uint_as_float(v) + bias, p.act); };
-            stmatrix_x4_trans(stage + st_off,
-                              pack16(f(va[o + 0], b0), f(va[o + 1], b0), p.fmt), pack16(f(va[o + 2], b1), f(va[o + 3], b1), p.fmt),
-                              pack16(f(va[o + 4], b0), f(va[o + 5], b0), p.fmt), pack16(f(va[o + 6], b1), f(va[o + 7], b1), p.fmt));
-            stmatrix_x4_trans(stage + st_off + 32,
-                              pack16(f(vb[o + 0], b2), f(vb[o + 1], b2), p.fmt), pack16(f(vb[o + 2], b3), f(vb[o + 3], b3), p.fmt),
-                              pack16(f(vb[o + 4], b2), f(vb[o + 5], b2), p.fmt), pack16(f(vb[o + 6], b3), f(vb[o + 7], b3), p.fmt));
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0 && tok_w + c * 16 < p.m_tok) {
-            const int t0 = tok_w + c * 16;
-            if (SCATTER) {
-              // reduce-scatter fused into the GEMM: the chunk goes to the rank that owns these
-              // tokens, into the slot reserved for this rank's partial sums (a store over NVLink)
-              const int owner = t0 / p.tok_per_owner;
-              tma_store_2d(&tmS->m[owner], stage, out_x, t0 - owner * p.tok_per_owner);
-            } else {
-              tma_store_2d_hint(&tmD, stage, out_x, t0, pol_stream);
-            }
-            tma_store_commit();
-          }
-        }
-      } else {
-        uint32_t ra[16], rb[16];
-        tmem_ld_32x16(t_acc, ra);
+          for (int ps = 0; ps < C::PASSES; ++ps) {
+            // window of this pass: RS = 1 -> chosen by w2 (already folded into t_acc / tok_w); RS = 2 -> by ps
+            const int win = (C::RS == 1) ? 0 : ps * (C::BN - 128);
+            const int cb = (C::RS == 1) ? c_begin : ps * C::SKIP_CHUNKS;
+            tmem_ld_16x256b_x16(t_acc + win, va);
+            tmem_ld_16x256b_x16(t_acc + win + (static_cast<uint32_t>(16) << 16), vb);
+            tmem_ld_wait();
+            if (ps == C::PASSES - 1) release_acc();
 #pragma unroll
-        for (int c = 0; c < NCH; ++c) {
-          tmem_ld_wait();
-          if (c + 1 < NCH) {
-            if (c & 1) tmem_ld_32x16(t_acc + (c + 1) * 16, ra);
-            else tmem_ld_32x16(t_acc + (c + 1) * 16, rb);
-          } else {
-            // every column of this warp's share has been read: hand the accumulator back
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_remote(leader_acce);
+            for (int c = 0; c < 8; ++c)
+              if (c >= cb) store_chunk16(&va[8 * c], &vb[8 * c], c, tok_w + win + c * 16, b0, b1, b2, b3);
           }
-          if (c & 1) epilogue_chunk<C::EPI>(rb, p, ycol, col_ok, tok_w + c * 16, bias_v, upper);
-          else epilogue_chunk<C::EPI>(ra, p, ycol, col_ok, tok_w + c * 16, bias_v, upper);
         }
       }
     }
-    if (C::RS == 1 && lane == 0) tma_store_wait_all<0>();
   }
 
   // ------------------------------------------------------------ teardown
@@ -604,18 +659,8 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
 template <class C>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(C::THREADS, 1)
 sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                        const __grid_constant__ CUtensorMap tmE, const __grid_constant__ CUtensorMap tmD,
-                        const PairParams p) {
-  pair_kernel_body<C, false>(tmA, tmB, tmE, tmD, nullptr, p);
-}
-
-// Same kernel with the scatter epilogue (tensor-parallel row-parallel GEMM).
-template <class C>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(C::THREADS, 1)
-sparse_gemm_pair_scatter_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                                const __grid_constant__ CUtensorMap tmE, const __grid_constant__ ScatterMaps tmS,
-                                const PairParams p) {
-  pair_kernel_body<C, true>(tmA, tmB, tmE, tmS.m[0], &tmS, p);
+                        const __grid_constant__ CUtensorMap tmE, const PairParams p) {
+  pair_kernel_body<C>(tmA, tmB, tmE, p);
 }
 
 template <class C>
@@ -629,7 +674,7 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
       return kErrCuda;
     attr_set[dev] = true;
   }
-  CUtensorMap tmA, tmB, tmE, tmD;
+  CUtensorMap tmA, tmB, tmE;
   const uint64_t kc = static_cast<uint64_t>(a.K) / 2;
   if (!make_map_2d(&tmA, a.values, a.n_out, kc, kc * 2, C::ROWS_CTA, C::BK / 2,
                    C::BK == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, a.fmt))
@@ -638,12 +683,6 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
                    CU_TENSOR_MAP_SWIZZLE_128B, a.fmt))
     return kErrTensorMap;
   if (!make_map_1d_u64(&tmE, a.meta, meta_bytes(a.n_out, a.K) / 8, 256)) return kErrTensorMap;
-  {
-    const int out_cols = (C::EPI == kEpiSwiGLU) ? a.n_out / 2 : a.n_out;
-    if (!make_map_2d(&tmD, a.y, a.m_tok, out_cols, static_cast<uint64_t>(a.ldy) * 2, 16, C::D_ROW_BYTES / 2,
-                     CU_TENSOR_MAP_SWIZZLE_NONE, a.fmt))
-      return kErrTensorMap;
-  }
   PairParams p;
   p.bias = a.bias;
   p.y = a.y;
@@ -658,12 +697,30 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
   p.fmt = a.fmt;
   p.act = a.act;
   p.tok_per_owner = 0;
-  p.band = pick_band(C::BN, a.K, p.num_n_blks);
+  for (int o = 0; o < 8; ++o) p.peer_y[o] = nullptr;
+  if (a.peer_y != nullptr) {      // row-parallel GEMM with the reduce-scatter fused into the epilogue
+    if (C::EPI != kEpiStore || a.tp < 2 || a.tp > 8 || a.tok_per_owner <= 0 || a.tok_per_owner % 16 != 0 ||
+        static_cast<long>(a.tok_per_owner) * a.tp < a.m_tok)
+      return kErrInvalid;
+    for (int o = 0; o < 8; ++o) {
+      void* base = a.peer_y[o < a.tp ? o : 0];
+      if (!base || (reinterpret_cast<uintptr_t>(base) & 15)) return kErrInvalid;
+      p.peer_y[o] = base;
+    }
+    p.tok_per_owner = a.tok_per_owner;
+  }
+  p.out_f32 = a.out_f32;
+  pick_order(a.n_out, a.m_tok, a.K, C::ROWS_TILE, C::BN, p.num_m_blks, p.num_n_blks, p);
+  if (g_force_order >= 0) {
+    p.order = g_force_order;
+    p.band = p.order ? pick_band(static_cast<long>(C::ROWS_TILE * 1.125 * a.K), p.num_m_blks)
+                     : pick_band(static_cast<long>(C::BN) * a.K * 2, p.num_n_blks);
+  }
   const int tiles = p.num_m_blks * p.num_n_blks;
   int pairs = a.num_sms / 2;
   if (pairs > tiles) pairs = tiles;
   if (pairs < 1) pairs = 1;
-  sparse_gemm_pair_kernel<C><<<2 * pairs, C::THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmE, tmD, p);
+  sparse_gemm_pair_kernel<C><<<2 * pairs, C::THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmE, p);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
 }
 
@@ -712,6 +769,10 @@ int dispatch_pair(const SparseGemmArgs& a, cudaStream_t stream) {
     case 1224: return launch_pair_cfg<PairCfg<224, 128, 4, 1, EPI>>(a, stream);
     case 1208: return launch_pair_cfg<PairCfg<208, 128, 4, 1, EPI>>(a, stream);
     case 1192: return launch_pair_cfg<PairCfg<192, 128, 4, 1, EPI>>(a, stream);
+    case 5240: return launch_pair_cfg<PairCfg<240, 128, 3, 2, EPI>>(a, stream);
+    case 5224: return launch_pair_cfg<PairCfg<224, 128, 3, 2, EPI>>(a, stream);
+    case 5208: return launch_pair_cfg<PairCfg<208, 128, 3, 2, EPI>>(a, stream);
+    case 5192: return launch_pair_cfg<PairCfg<192, 128, 3, 2, EPI>>(a, stream);
     case 2192: return launch_pair_cfg<PairCfg<192, 64, 6, 2, EPI>>(a, stream);
     case 2208: return launch_pair_cfg<PairCfg<208, 64, 6, 2, EPI>>(a, stream);
     case 2224: return launch_pair_cfg<PairCfg<224, 64, 6, 2, EPI>>(a, stream);
@@ -722,62 +783,13 @@ int dispatch_pair(const SparseGemmArgs& a, cudaStream_t stream) {
 
 }  // namespace
 
-int pick_pair_variant(int n_out, int m_tok, int K, int num_sms) {
-  return pick_pair_variant_impl(n_out, m_tok, K, num_sms / 2 > 0 ? num_sms / 2 : 1);
+void set_pair_tuning(int l2_band_mb, int force_order) {
+  if (l2_band_mb > 0) g_l2_band_mb = l2_band_mb;
+  g_force_order = force_order;
 }
 
-int launch_sparse_gemm_pair_scatter(const SparseGemmArgs& a, void* const* peer_slots, int tp, int tok_per_owner,
-                                    cudaStream_t stream) {
-  using C = PairCfg<256, 128, 4, 1, kEpiStore>;
-  if (a.K % 64 != 0 || a.m_tok <= 0 || a.n_out <= 0 || a.n_out % 8 != 0 || a.ldx % 8 != 0) return kErrInvalid;
-  if (tp < 2 || tp > 8 || tok_per_owner <= 0 || tok_per_owner % 16 != 0 || tok_per_owner * tp < a.m_tok)
-    return kErrInvalid;
-  static bool attr_set[16] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 16 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(sparse_gemm_pair_scatter_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             C::SMEM_BYTES) != cudaSuccess)
-      return kErrCuda;
-    attr_set[dev] = true;
-  }
-  CUtensorMap tmA, tmB, tmE;
-  ScatterMaps tmS;
-  const uint64_t kc = static_cast<uint64_t>(a.K) / 2;
-  if (!make_map_2d(&tmA, a.values, a.n_out, kc, kc * 2, C::ROWS_CTA, C::BK / 2, CU_TENSOR_MAP_SWIZZLE_128B, a.fmt))
-    return kErrTensorMap;
-  if (!make_map_2d(&tmB, a.x, a.m_tok, a.K, static_cast<uint64_t>(a.ldx) * 2, C::HALF_N, 64,
-                   CU_TENSOR_MAP_SWIZZLE_128B, a.fmt))
-    return kErrTensorMap;
-  if (!make_map_1d_u64(&tmE, a.meta, meta_bytes(a.n_out, a.K) / 8, 256)) return kErrTensorMap;
-  for (int o = 0; o < 8; ++o) {
-    void* base = peer_slots[o < tp ? o : 0];
-    if (!base || (reinterpret_cast<uintptr_t>(base) & 15)) return kErrInvalid;
-    if (!make_map_2d(&tmS.m[o], base, tok_per_owner, a.n_out, static_cast<uint64_t>(a.n_out) * 2, 16,
-                     C::D_ROW_BYTES / 2, CU_TENSOR_MAP_SWIZZLE_NONE, a.fmt))
-      return kErrTensorMap;
-  }
-  PairParams p;
-  p.bias = a.bias;
-  p.y = nullptr;
-  p.status = a.status;
-  p.n_out = a.n_out;
-  p.m_tok = a.m_tok;
-  p.K = a.K;
-  p.ldy = a.n_out;
-  p.num_m_blks = (a.n_out + C::ROWS_TILE - 1) / C::ROWS_TILE;
-  p.num_n_blks = (a.m_tok + C::BN - 1) / C::BN;
-  p.k_tiles128 = (a.K + 127) / 128;
-  p.fmt = a.fmt;
-  p.act = a.act;
-  p.tok_per_owner = tok_per_owner;
-  p.band = pick_band(C::BN, a.K, p.num_n_blks);
-  const int tiles = p.num_m_blks * p.num_n_blks;
-  int pairs = a.num_sms / 2;
-  if (pairs > tiles) pairs = tiles;
-  if (pairs < 1) pairs = 1;
-  sparse_gemm_pair_scatter_kernel<C><<<2 * pairs, C::THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmE, tmS, p);
-  return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
+int pick_pair_variant(int n_out, int m_tok, int K, int num_sms) {
+  return pick_pair_variant_impl(n_out, m_tok, K, num_sms / 2 > 0 ? num_sms / 2 : 1);
 }
 
 int launch_sparse_gemm_pair(const SparseGemmArgs& a, cudaStream_t stream) {
@@ -787,6 +799,8 @@ int launch_sparse_gemm_pair(const SparseGemmArgs& a, cudaStream_t stream) {
        reinterpret_cast<uintptr_t>(a.meta) | reinterpret_cast<uintptr_t>(a.y)) & 15)
     return kErrInvalid;
   if (a.ldy % 8 != 0) return kErrInvalid;
+  if ((a.out_f32 || a.peer_y != nullptr) && a.epi != kEpiStore) return kErrInvalid;
+  if (a.y == nullptr && a.peer_y == nullptr) return kErrInvalid;
   if (a.epi == kEpiSwiGLU) {
     if (a.n_out % 32 != 0 || (a.n_out / 2) % 8 != 0) return kErrInvalid;
     return dispatch_pair<kEpiSwiGLU>(a, stream);

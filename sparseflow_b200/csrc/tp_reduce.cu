@@ -1,12 +1,6 @@
-// Second half of the fused tensor-parallel down projection.  After every rank's GEMM epilogue has
-// stored its partial sums of token block r into rank r's receive slots (one slot per source rank),
-// rank r adds the slots in fp32 and writes the finished block into the output tensor of EVERY rank
-// : the all-gather is fused into the reduction, so the partial sums cross NVLink once and the
-// finished block once.  The finished block is written either with plain 16-byte stores to each rank's
-// peer-mapped memory (tp - 1 copies leave this GPU) or, when the output tensor has a switch-replicated
-// mapping, with multimem.st (one copy leaves this GPU and NVSwitch fans it out).
-// HBM / NVLink bound: reads tp * rows * cols * 2 B locally, writes rows * cols * 2 B to each rank.
-// No kernel here waits on another GPU: ordering is by stream-ordered barriers between launches.
+// Exchange kernels of the tensor-parallel FFN: the reduction of the row-parallel GEMM's partial sums across ranks
+// and the replication of the finished token blocks, one launch per rank, over NVLink peer stores or through
+// NVSwitch (multimem).  HBM / NVLink bound.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -46,57 +40,27 @@ __device__ __forceinline__ void store_all_ranks(uint4* mc, const uint4& v) {
                : "memory");
 }
 
-template <bool BF16>
-__global__ void __launch_bounds__(256) reduce_allgather_kernel(const uint4* slots, int tp, size_t vec_per_slot,
-                                                               int vec_per_row, PeerOut out, uint4* mc_out,
-                                                               const uint16_t* bias) {
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < vec_per_slot;
-       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int s = 0; s < tp; ++s) add8<BF16>(acc, __ldg(slots + s * vec_per_slot + i));
-    if (bias) {
-      const int c0 = static_cast<int>(i % vec_per_row) * 8;
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        acc[j] += BF16 ? __uint_as_float(static_cast<uint32_t>(bias[c0 + j]) << 16)
-                       : __half2float(__ushort_as_half(bias[c0 + j]));
-    }
-    uint4 o;
-    uint32_t* ow = &o.x;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (BF16) {
-        const __nv_bfloat162 v = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-        ow[j] = *reinterpret_cast<const uint32_t*>(&v);
-      } else {
-        const __half2 v = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
-        ow[j] = *reinterpret_cast<const uint32_t*>(&v);
-      }
-    }
-    if (mc_out != nullptr) store_all_ranks(mc_out + i, o);     // the block leaves this GPU once
-    else
-      for (int d = 0; d < tp; ++d) out.p[d][i] = o;
-  }
-}
-
-// ---------------------------------------------------------------- exchange through NVSwitch, one kernel
+// ---------------------------------------------------------------- exchange step, one kernel per rank
 //
-// The whole exchange step of the row-parallel GEMM in ONE launch per rank: every rank has written its
-// partial output [M, cols] into its own copy of a symmetric buffer; this kernel waits until all ranks
-// have done so, sums its own token block ACROSS ranks inside the switch (multimem.ld_reduce, fp32
-// accumulation of the 16-bit partials), adds the bias, rounds once and writes the finished block
-// into every rank's output with multimem.st, then waits until every rank has finished.  Compared
-// with "scatter in the GEMM epilogue + barrier + reduce kernel + barrier" it moves the same bytes
-// out of each GPU but needs one launch instead of four and reads 1/tp of the partials instead of
-// all of them through this GPU's memory.
+// The reduction + all-gather of the row-parallel GEMM in ONE launch per rank, with the cross-GPU ordering inside the
+// kernel.  Four forms (MODE):
+//   3  "push": every rank's GEMM epilogue has already stored its partial sums of token block r into rank r's receive
+//      slots (one slot per source rank, local memory here).  This kernel waits until all ranks' GEMMs are done, adds
+//      the tp slots in fp32 (slots are FLOAT or 16-bit), adds the bias, rounds ONCE and stores the finished block
+//      into every rank's output with plain 16-byte peer stores (or one multimem.st when a switch-replicated mapping
+//      of the output is given).  Needs no multicast support.
+//   1/2 "pull through the switch": every rank wrote its partial output into its own copy of a symmetric buffer; this
+//      rank's block is summed across ranks inside NVSwitch (multimem.ld_reduce; 16-bit partials with fp32
+//      accumulation, or FLOAT partials) and written to every rank with multimem.st.
+//   0  all-gather of one local 16-bit block per rank (e.g. the activations each rank uploaded).
+// Every form returns only when every rank has finished, so the caller's next kernel may overwrite the buffers.
 //
-// Cross-GPU ordering uses flag words in symmetric memory, one set per CTA: CTA b of rank r stores
-// the launch's epoch into slot [b][r] of every rank (st.release.sys) and polls its own slots
-// [b][0..tp) (ld.acquire.sys) -- CTA b talks only to CTA b of the other ranks, so every rank must
-// launch the same grid.  Epochs increase by one per launch and are never reset.  Every poll loop is
-// bounded: after kPeerWaitLimitNs it records (2 << 8) | phase in the status word, the CTA skips its
-// remaining work and waits, and the kernel returns.
-// No load of any kind names a peer's memory directly; the multicast address is the only remote path.
+// Cross-GPU ordering uses flag words in symmetric memory, one set per CTA: CTA b of rank r stores the launch's epoch
+// into slot [b][r] of every rank (st.release.sys) and polls its own slots [b][0..tp) (ld.acquire.sys) -- CTA b
+// talks only to CTA b of the other ranks, so every rank launches the same grid.  Epochs increase by one per launch
+// and are never reset.  Every poll loop is bounded: after kPeerWaitLimitNs it records (2 << 8) | phase in the
+// status word, the CTA skips its remaining work and waits, and the kernel returns.
+// No load of any kind names a peer's memory directly: remote data arrives by peers' stores or through multimem.
 constexpr unsigned long long kPeerWaitLimitNs = 2000000000ull;
 constexpr int kExchangeCtas = 148;
 constexpr int kExchangeThreads = 512;
@@ -121,7 +85,7 @@ __device__ __forceinline__ unsigned long long timer_ns() {
 }
 
 // Threads 0..tp-1 of the CTA: announce `epoch` in slot [cta][rank] of every rank, then wait until all
-// of this rank's slots [cta][0..tp) have reached it.  Returns false (warp-uniform per thread) on timeout.
+// of this rank's slots [cta][0..tp) have reached it.  Returns false on timeout.
 __device__ __forceinline__ bool cta_rank_barrier(const FlagPeers& peers, uint32_t* local, int region_off, int tp,
                                                  int rank, uint32_t epoch, int* status, int phase,
                                                  unsigned long long limit_ns) {
@@ -144,67 +108,143 @@ __device__ __forceinline__ bool cta_rank_barrier(const FlagPeers& peers, uint32_
   return ok;
 }
 
-template <bool BF16, bool REDUCE>
-__global__ void __launch_bounds__(kExchangeThreads, 1)
-switch_exchange_kernel(const uint4* src, uint4* mc_dst, size_t vec, int vec_per_row, const uint16_t* bias, FlagPeers peers,
-                       uint32_t* local_flags, int tp, int rank, uint32_t epoch, int* status, unsigned long long limit_ns) {
+template <bool BF16>
+__device__ __forceinline__ uint4 round8(const float (&acc)[8]) {
+  uint4 o;
+  uint32_t* ow = &o.x;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (BF16) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      ow[j] = *reinterpret_cast<const uint32_t*>(&h);
+    } else {
+      const __half2 h = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+      ow[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+  }
+  return o;
+}
+
+struct ExchangeArgs {
+  const void* src;        // MODE 0: local block; 1/2: multicast address of the block; 3: local slots [tp][slot_units]
+  uint4* mc_dst;          // multicast address of the destination block, or null (MODE 0 / 3: peer stores instead)
+  PeerOut out;            // destination block in every rank's buffer (used when mc_dst is null)
+  size_t vec;             // 16-byte units of OUTPUT (8 values each) in the block
+  size_t slot_units;      // MODE 3: distance between two source ranks' slots, in output units
+  int vec_per_row;
+  int slots_f32;          // MODE 3: slots hold floats
+  const uint16_t* bias;
+  FlagPeers peers;
+  uint32_t* local_flags;
+  int tp, rank;
+  uint32_t epoch;
+  int* status;
+  unsigned long long limit_ns;
+};
+
+template <bool BF16, int MODE>
+__global__ void __launch_bounds__(kExchangeThreads, 1) exchange_kernel(const ExchangeArgs a) {
   __shared__ int failed;
   if (threadIdx.x == 0) failed = 0;
   __syncthreads();
   // ---- every rank's source data is complete (its producer kernel precedes this one on its stream)
-  if (!cta_rank_barrier(peers, local_flags, 0, tp, rank, epoch, status, 1, limit_ns)) failed = 1;
+  if (!cta_rank_barrier(a.peers, a.local_flags, 0, a.tp, a.rank, a.epoch, a.status, 1, a.limit_ns)) failed = 1;
   __syncthreads();
   if (!failed) {
+    constexpr int U = (MODE == 3) ? 1 : 4;
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-    for (size_t i0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i0 < vec; i0 += 4 * stride) {
-      uint4 v[4];
+    for (size_t i0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i0 < a.vec; i0 += U * stride) {
+      uint4 v[U], w[U];
+      float acc3[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < U; ++u) {
         const size_t i = i0 + u * stride;
-        if (i < vec) {
-          if (REDUCE) {
-            if (BF16)
-              asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
-                           : "l"(src + i)
-                           : "memory");
-            else
-              asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
-                           : "l"(src + i)
-                           : "memory");
+        if (i >= a.vec) continue;
+        if (MODE == 3) {
+          // all tp slots' loads are issued before the first add (local HBM / L2 reads)
+          uint4 x0[8], x1[8];
+          if (a.slots_f32) {
+            const uint4* s = static_cast<const uint4*>(a.src) + 2 * i;
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+              if (r < a.tp) {
+                x0[r] = __ldcs(s + 2 * r * a.slot_units);
+                x1[r] = __ldcs(s + 2 * r * a.slot_units + 1);
+              }
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+              if (r < a.tp) {
+                acc3[0] += __uint_as_float(x0[r].x); acc3[1] += __uint_as_float(x0[r].y);
+                acc3[2] += __uint_as_float(x0[r].z); acc3[3] += __uint_as_float(x0[r].w);
+                acc3[4] += __uint_as_float(x1[r].x); acc3[5] += __uint_as_float(x1[r].y);
+                acc3[6] += __uint_as_float(x1[r].z); acc3[7] += __uint_as_float(x1[r].w);
+              }
           } else {
-            v[u] = __ldg(src + i);
+            const uint4* s = static_cast<const uint4*>(a.src) + i;
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+              if (r < a.tp) x0[r] = __ldcs(s + r * a.slot_units);
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+              if (r < a.tp) add8<BF16>(acc3, x0[r]);
           }
+        } else if (MODE == 2) {
+          const uint4* s = static_cast<const uint4*>(a.src) + 2 * i;
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                       : "l"(s)
+                       : "memory");
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(w[u].x), "=r"(w[u].y), "=r"(w[u].z), "=r"(w[u].w)
+                       : "l"(s + 1)
+                       : "memory");
+        } else if (MODE == 1) {
+          const uint4* s = static_cast<const uint4*>(a.src) + i;
+          if (BF16)
+            asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                         : "l"(s)
+                         : "memory");
+          else
+            asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                         : "l"(s)
+                         : "memory");
+        } else {
+          v[u] = __ldg(static_cast<const uint4*>(a.src) + i);
         }
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < U; ++u) {
         const size_t i = i0 + u * stride;
-        if (i < vec) {
-          uint4 o = v[u];
-          if (REDUCE && bias) {
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            add8<BF16>(acc, o);
-            const int c0 = static_cast<int>(i % vec_per_row) * 8;
-            uint32_t* ow = &o.x;
+        if (i >= a.vec) continue;
+        uint4 o = v[u];
+        if (MODE >= 2 || (MODE == 1 && a.bias)) {
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          if (MODE == 3) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float a = acc[2 * j], b = acc[2 * j + 1];
-              if (BF16) {
-                a += __uint_as_float(static_cast<uint32_t>(bias[c0 + 2 * j]) << 16);
-                b += __uint_as_float(static_cast<uint32_t>(bias[c0 + 2 * j + 1]) << 16);
-                const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-                ow[j] = *reinterpret_cast<const uint32_t*>(&h);
-              } else {
-                a += __half2float(__ushort_as_half(bias[c0 + 2 * j]));
-                b += __half2float(__ushort_as_half(bias[c0 + 2 * j + 1]));
-                const __half2 h = __floats2half2_rn(a, b);
-                ow[j] = *reinterpret_cast<const uint32_t*>(&h);
-              }
-            }
+            for (int j = 0; j < 8; ++j) acc[j] = acc3[j];
+          } else if (MODE == 2) {
+            const uint32_t f[8] = {v[u].x, v[u].y, v[u].z, v[u].w, w[u].x, w[u].y, w[u].z, w[u].w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = __uint_as_float(f[j]);
+          } else {
+            add8<BF16>(acc, o);
           }
-          store_all_ranks(mc_dst + i, o);
+          if (a.bias) {
+            const int c0 = static_cast<int>(i % a.vec_per_row) * 8;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              acc[j] += BF16 ? __uint_as_float(static_cast<uint32_t>(a.bias[c0 + j]) << 16)
+                             : __half2float(__ushort_as_half(a.bias[c0 + j]));
+          }
+          o = round8<BF16>(acc);
+        }
+        if (a.mc_dst != nullptr) store_all_ranks(a.mc_dst + i, o);
+        else {
+#pragma unroll
+          for (int d = 0; d < 8; ++d)
+            if (d < a.tp) a.out.p[d][i] = o;
         }
       }
     }
@@ -212,67 +252,57 @@ switch_exchange_kernel(const uint4* src, uint4* mc_dst, size_t vec, int vec_per_
   // ---- this CTA's stores are ordered before its exit flag; then every rank has finished
   __threadfence_system();
   __syncthreads();
-  if (!failed) cta_rank_barrier(peers, local_flags, kExchangeCtas * 8, tp, rank, epoch, status, 2, limit_ns);
+  if (!failed) cta_rank_barrier(a.peers, a.local_flags, kExchangeCtas * 8, a.tp, a.rank, a.epoch, a.status, 2, a.limit_ns);
 }
 
 }  // namespace
 
-int launch_switch_exchange(bool reduce, const void* src, void* mc_dst, int rows, int cols, int fmt, const void* bias,
-                           void* const* peer_flags, int tp, int rank, unsigned epoch, int* status, cudaStream_t stream) {
+int launch_exchange(int mode, const void* src, void* mc_dst, void* const* peer_dst, int rows, int cols, int slot_rows,
+                    int slots_f32, int fmt, const void* bias, void* const* peer_flags, int tp, int rank, unsigned epoch,
+                    int* status, cudaStream_t stream) {
   // rows == 0: this rank contributes no block but still takes part in the two barriers
-  if (!src || !mc_dst || !peer_flags || !status || rows < 0 || cols <= 0 || cols % 8 != 0) return kErrInvalid;
-  if (tp < 2 || tp > 8 || rank < 0 || rank >= tp || epoch == 0) return kErrInvalid;
+  if (!src || !peer_flags || !status || rows < 0 || cols <= 0 || cols % 8 != 0) return kErrInvalid;
+  if (!mc_dst && !peer_dst) return kErrInvalid;
+  if (tp < 2 || tp > 8 || rank < 0 || rank >= tp || epoch == 0 || mode < 0 || mode > 3) return kErrInvalid;
   if (fmt != kF16 && fmt != kBF16) return kErrInvalid;
   if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(mc_dst)) & 15) return kErrInvalid;
-  if (!reduce && bias) return kErrInvalid;
-  FlagPeers peers = {};
+  if (mode == 0 && bias) return kErrInvalid;
+  if ((mode == 1 || mode == 2) && !mc_dst) return kErrInvalid;
+  if (mode == 3 && slot_rows < rows) return kErrInvalid;
+  ExchangeArgs a = {};
   for (int d = 0; d < 8; ++d) {
     void* q = peer_flags[d < tp ? d : 0];
     if (!q || (reinterpret_cast<uintptr_t>(q) & 3)) return kErrInvalid;
-    peers.p[d] = static_cast<uint32_t*>(q);
+    a.peers.p[d] = static_cast<uint32_t*>(q);
+    if (!mc_dst) {
+      void* o = peer_dst[d < tp ? d : 0];
+      if (!o || (reinterpret_cast<uintptr_t>(o) & 15)) return kErrInvalid;
+      a.out.p[d] = static_cast<uint4*>(o);
+    }
   }
-  uint32_t* local = peers.p[rank];
-  const size_t vec = static_cast<size_t>(rows) * cols / 8;
-  const uint4* s4 = static_cast<const uint4*>(src);
-  uint4* d4 = static_cast<uint4*>(mc_dst);
-  const uint16_t* b16 = static_cast<const uint16_t*>(bias);
-  if (reduce) {
-    if (fmt == kBF16)
-      switch_exchange_kernel<true, true><<<kExchangeCtas, kExchangeThreads, 0, stream>>>(
-          s4, d4, vec, cols / 8, b16, peers, local, tp, rank, epoch, status, kPeerWaitLimitNs);
-    else
-      switch_exchange_kernel<false, true><<<kExchangeCtas, kExchangeThreads, 0, stream>>>(
-          s4, d4, vec, cols / 8, b16, peers, local, tp, rank, epoch, status, kPeerWaitLimitNs);
-  } else {
-    switch_exchange_kernel<true, false><<<kExchangeCtas, kExchangeThreads, 0, stream>>>(
-        s4, d4, vec, cols / 8, nullptr, peers, local, tp, rank, epoch, status, kPeerWaitLimitNs);
-  }
-  return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
-}
-
-int launch_reduce_allgather(const void* slots, int tp, int rows, int cols, void* const* peer_out_blocks,
-                            void* switch_out_block, int fmt, const void* bias, cudaStream_t stream) {
-  if (!slots || tp < 1 || tp > 8 || rows <= 0 || cols <= 0 || cols % 8 != 0) return kErrInvalid;
-  if (fmt != kF16 && fmt != kBF16) return kErrInvalid;
-  if (!peer_out_blocks && !switch_out_block) return kErrInvalid;
-  if (reinterpret_cast<uintptr_t>(switch_out_block) & 15) return kErrInvalid;
-  PeerOut out = {};
-  for (int d = 0; d < 8 && switch_out_block == nullptr; ++d) {
-    void* q = peer_out_blocks[d < tp ? d : 0];
-    if (!q || (reinterpret_cast<uintptr_t>(q) & 15)) return kErrInvalid;
-    out.p[d] = static_cast<uint4*>(q);
-  }
-  const size_t vec = static_cast<size_t>(rows) * cols / 8;
-  size_t blocks = (vec + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
-  if (fmt == kBF16)
-    reduce_allgather_kernel<true><<<static_cast<int>(blocks), 256, 0, stream>>>(
-        static_cast<const uint4*>(slots), tp, vec, cols / 8, out, static_cast<uint4*>(switch_out_block),
-        static_cast<const uint16_t*>(bias));
-  else
-    reduce_allgather_kernel<false><<<static_cast<int>(blocks), 256, 0, stream>>>(
-        static_cast<const uint4*>(slots), tp, vec, cols / 8, out, static_cast<uint4*>(switch_out_block),
-        static_cast<const uint16_t*>(bias));
+  a.src = src;
+  a.mc_dst = static_cast<uint4*>(mc_dst);
+  a.vec = static_cast<size_t>(rows) * cols / 8;
+  a.slot_units = static_cast<size_t>(slot_rows) * cols / 8;
+  a.vec_per_row = cols / 8;
+  a.slots_f32 = slots_f32;
+  a.bias = static_cast<const uint16_t*>(bias);
+  a.local_flags = a.peers.p[rank];
+  a.tp = tp;
+  a.rank = rank;
+  a.epoch = epoch;
+  a.status = status;
+  a.limit_ns = kPeerWaitLimitNs;
+  const bool bf = fmt == kBF16;
+#define SFB_LAUNCH_EXCHANGE(BF, MODE) exchange_kernel<BF, MODE><<<kExchangeCtas, kExchangeThreads, 0, stream>>>(a)
+  if (mode == 0) SFB_LAUNCH_EXCHANGE(true, 0);
+  else if (mode == 1 && bf) SFB_LAUNCH_EXCHANGE(true, 1);
+  else if (mode == 1) SFB_LAUNCH_EXCHANGE(false, 1);
+  else if (mode == 2 && bf) SFB_LAUNCH_EXCHANGE(true, 2);
+  else if (mode == 2) SFB_LAUNCH_EXCHANGE(false, 2);
+  else if (bf) SFB_LAUNCH_EXCHANGE(true, 3);
+  else SFB_LAUNCH_EXCHANGE(false, 3);
+#undef SFB_LAUNCH_EXCHANGE
   return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
 }
 

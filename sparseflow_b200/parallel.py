@@ -9,11 +9,11 @@ a multiple of 64 are zero-padded (zero gate/up rows give hidden == 0, zero down 
 
 Two implementations of the exchange step:
 * ``TensorParallelFFN``: down GEMM, then NCCL all-reduce (the baseline);
-* ``FusedTensorParallelFFN``: the down GEMM's epilogue TMA-stores each partial token block straight
-  into the owning rank's receive slot over NVLink (reduce-scatter fused into the GEMM), then one
-  kernel sums the slots in fp32 and writes the finished block into every rank's output (all-gather
-  fused into the reduction).  Buffers are torch symmetric memory; ranks are ordered by its
-  stream-ordered barrier between the two kernels, so no kernel ever waits on another GPU.
+* ``FusedTensorParallelFFN``: the down GEMM's epilogue stores each partial token block straight into the
+  owning rank's receive slot over NVLink (reduce-scatter fused into the GEMM), then one kernel per rank
+  sums the slots in fp32 and writes the finished block into every rank's output (all-gather fused into
+  the reduction), with the ordering across ranks inside that kernel (flag words in symmetric memory,
+  bounded polls).  Buffers are torch symmetric memory.
 
 One process per GPU; torch.distributed carries the collective.  With ``chunks > 1`` the token
 dimension is split and the all-reduce of chunk i overlaps the GEMMs of chunk i+1 on a second stream.
@@ -130,21 +130,29 @@ class TensorParallelFFN:
 class FusedTensorParallelFFN:
     """TP FFN whose exchange step runs in this library's own kernels over NVLink / NVSwitch.
 
-    ``exchange="switch"`` (the default where the fabric offers switch-replicated mappings of symmetric memory):
-    the down GEMM writes this rank's partial sums into its own copy of a symmetric buffer, then ONE kernel per
-    rank does barrier -> in-switch reduction of its own token block (``multimem.ld_reduce``, fp32 accumulation) ->
-    bias -> ``multimem.st`` of the finished block into every rank's output -> barrier.  Three launches per step.
+    ``exchange="push"`` (default): the down GEMM's epilogue stores every partial token block straight into the owning
+    rank's receive slot over NVLink while the GEMM runs (reduce-scatter fused into the GEMM, tile by tile); then ONE
+    kernel per rank waits for all ranks' GEMMs, adds the slots in fp32, adds the bias, rounds once and stores the
+    finished block into every rank's output (all-gather fused into the reduction), and returns when every rank is
+    done.  Three launches per step, plain peer stores only, no multicast needed.
 
-    ``exchange="scatter"``: the down GEMM's epilogue TMA-stores each partial token block into the owning rank's
-    receive slot (reduce-scatter fused into the GEMM), a second kernel sums the slots and writes the finished block
-    to every rank with peer stores; two stream-ordered symmetric-memory barriers order them.  Needs no multicast
-    mapping; kept for fabrics without one.
+    ``exchange="switch"``: the down GEMM writes this rank's partial sums into its own copy of a symmetric buffer; one
+    kernel per rank sums its token block across ranks INSIDE NVSwitch (``multimem.ld_reduce``) and writes the finished
+    block to every rank with ``multimem.st``.  Needs switch-replicated (multicast) symmetric memory.  ``chunks`` cuts
+    the down GEMM and this exchange into token chunks, the exchange of chunk c running on a side stream beside the
+    GEMM of chunk c + 1.
+
+    ``partial_dtype``: ``"fp32"`` (default) keeps every rank's partial sums in fp32 until they have been added, so the
+    output is rounded to 16 bits once, as on one GPU, and meets the single-GPU error bound; ``"16bit"`` (the weight
+    dtype) halves the bytes of the reduction, but every partial then carries its own rounding and a few outputs per
+    million end up just outside that bound (measured 1.0e-2 .. 1.3e-2 against 1e-2).
 
     The result of ``forward`` is a view of a symmetric buffer that peers write into: see ``forward``.
     """
 
     def __init__(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, max_tokens: int, group=None,
-                 down_bias: Optional[torch.Tensor] = None, use_switch_stores: bool = False, exchange: str = "auto"):
+                 down_bias: Optional[torch.Tensor] = None, exchange: str = "push", partial_dtype: str = "fp32",
+                 chunks: int = 1, out_multicast: bool = False):
         import ctypes as C
         import torch.distributed._symmetric_memory as symm_mem
         from . import _lib, ops
@@ -154,8 +162,13 @@ class FusedTensorParallelFFN:
         self.rank = dist.get_rank(self.group)
         if not 2 <= self.tp <= 8:
             raise ValueError("fused tensor-parallel FFN needs 2..8 ranks")
-        if exchange not in ("auto", "switch", "scatter"):
-            raise ValueError("exchange must be 'auto', 'switch' or 'scatter'")
+        if exchange not in ("push", "switch"):
+            raise ValueError("exchange must be 'push' or 'switch'")
+        if partial_dtype not in ("fp32", "16bit", "bf16", "fp16"):
+            raise ValueError("partial_dtype must be 'fp32' or '16bit'")
+        self.exchange = exchange
+        self.partial_f32 = partial_dtype == "fp32"
+        self.chunks = max(1, int(chunks)) if exchange == "switch" else 1
         self.I, self.H = gate.shape
         g, u, d = shard_ffn_weights(gate, up, down, self.tp, self.rank)
         self.Ip = g.shape[0]
@@ -164,79 +177,108 @@ class FusedTensorParallelFFN:
         self.down_bias = down_bias
         self.dtype = gate.dtype
         dev = gate.device
+        self.device = dev
         self.tok_per_owner = block_rows(max_tokens, self.tp)
         self.max_tokens = max_tokens
-        Mo, H = self.tok_per_owner, self.H
+        Mo, H, tp = self.tok_per_owner, self.H, self.tp
         self.row_bytes = H * 2
+        self.pbytes = H * (4 if self.partial_f32 else 2)          # bytes per row of a partial-sum buffer
         VP = C.c_void_p * 8
         self._VP = VP
+        pdtype = torch.float32 if self.partial_f32 else self.dtype
+        self._symm = symm_mem
+
+        def ptrs(handle):
+            return [int(p) for p in handle.buffer_ptrs]
         # the replicated output [tp * tok_per_owner, H]
-        self.out = symm_mem.empty((self.tp * Mo, H), dtype=self.dtype, device=dev)
+        self.out = symm_mem.empty((tp * Mo, H), dtype=self.dtype, device=dev)
         self.h_out = symm_mem.rendezvous(self.out, self.group)
-        self.out_ptrs = [int(p) for p in self.h_out.buffer_ptrs]
+        self.out_ptrs = ptrs(self.h_out)
         self.mc_out = int(getattr(self.h_out, "multicast_ptr", 0) or 0)
-        self.exchange = exchange
-        if exchange == "auto":
-            self.exchange = "switch" if self.mc_out else "scatter"
-        if self.exchange == "switch":
-            # partial sums of every rank (same offsets), the gathered activations, and the flag words
-            self.partial = symm_mem.empty((self.tp * Mo, H), dtype=self.dtype, device=dev)
+        self.out_multicast = bool(out_multicast and self.mc_out)
+        if exchange == "switch":
+            # every rank's partial sums, same offsets on every rank
+            self.partial = symm_mem.empty((tp * Mo, H), dtype=pdtype, device=dev)
             self.h_partial = symm_mem.rendezvous(self.partial, self.group)
             self.mc_partial = int(getattr(self.h_partial, "multicast_ptr", 0) or 0)
             if not self.mc_out or not self.mc_partial:
                 raise RuntimeError("exchange='switch' needs switch-replicated (multicast) symmetric memory")
-            self.flags = symm_mem.empty((self.L.sfb200_tp_flag_words(),), dtype=torch.int32, device=dev)
-            self.flags.zero_()
-            self.h_flags = symm_mem.rendezvous(self.flags, self.group)
-            self.peer_flags = VP(*[int(self.h_flags.buffer_ptrs[r]) if r < self.tp else None for r in range(8)])
-            self.epoch = 0
-            self.x_full = None       # symmetric copy of the activations, created by forward_from_shards
-            torch.cuda.synchronize(dev)
-            dist.barrier(self.group)           # every rank's flags are zero before anyone signals
         else:
-            # receive slots [source rank][tok_per_owner, H]
-            self.recv = symm_mem.empty((self.tp, Mo, H), dtype=self.dtype, device=dev)
+            # receive slots [source rank][tok_per_owner, H]: rank s stores its partial sums of MY token block into slot s
+            self.recv = symm_mem.empty((tp, Mo, H), dtype=pdtype, device=dev)
             self.h_recv = symm_mem.rendezvous(self.recv, self.group)
-            self.recv_ptrs = [int(p) for p in self.h_recv.buffer_ptrs]
-            # Optional: the all-gather half through NVSwitch-replicated stores.  Off by default: the 16-byte
-            # switch stores measured slower than plain peer stores at 2 ranks (0.059 vs 0.037 ms) and at 4.
-            self.switch_out_base = self.mc_out if use_switch_stores else 0
-        self.switch_out = self.mc_out if (self.exchange == "switch" or use_switch_stores) else 0
+            self.recv_ptrs = ptrs(self.h_recv)
+        # flag words: one array for the exchange kernels (which may run on the side stream), one for the all-gather of
+        # the activations (main stream); each has its own epoch counter
+        nflag = self.L.sfb200_tp_flag_words()
+        self.flags = symm_mem.empty((2 * nflag,), dtype=torch.int32, device=dev)
+        self.flags.zero_()
+        self.h_flags = symm_mem.rendezvous(self.flags, self.group)
+        fp = ptrs(self.h_flags)
+        self.peer_flags = VP(*[fp[r] if r < tp else None for r in range(8)])
+        self.peer_flags_x = VP(*[fp[r] + 4 * nflag if r < tp else None for r in range(8)])
+        self.epoch = 0
+        self.epoch_x = 0
+        self.comm_stream = torch.cuda.Stream(device=dev) if self.chunks > 1 else None
+        self.x_full = None       # symmetric copy of the activations, created by forward_from_shards
         self.hidden = torch.empty((max_tokens, self.Ip), dtype=self.dtype, device=dev)
         self.kernel_launches = 0
+        torch.cuda.synchronize(dev)
+        dist.barrier(self.group)           # every rank's flags are zero before anyone signals
+
+    # ------------------------------------------------------------------ who computes what
+    def _chunk_spans(self, M: int):
+        """Token ranges of the down GEMM / exchange pipeline.  Chunks are multiples of 256 tokens (whole GEMM tiles)
+        and of 16 * tp (so that every chunk splits into whole owner blocks); otherwise one span."""
+        n = self.chunks
+        if n > 1:
+            step = -(-(-(-M // n)) // 256) * 256
+            if step % (16 * self.tp) == 0 and step < M:
+                return [(lo, min(M, lo + step)) for lo in range(0, M, step)]
+        return [(0, M)]
+
+    def finished_rows(self, M: int):
+        """The token ranges whose finished values THIS rank produces in a step of M tokens (one per chunk)."""
+        out = []
+        for lo, hi in self._chunk_spans(M):
+            mo_c = block_rows(hi - lo, self.tp)
+            a, b = min(hi, lo + self.rank * mo_c), min(hi, lo + (self.rank + 1) * mo_c)
+            if b > a:
+                out.append((a, b))
+        return out
 
     def owned_rows(self, M: int) -> Tuple[int, int]:
-        """Half-open range of the token rows whose finished values THIS rank computes in a step of M tokens."""
+        """Half-open range of the token rows that THIS rank contributes in ``forward_from_shards``."""
         return owned_rows(M, self.tp, self.rank)
 
+    def _cast(self, arr):
+        return self.C.cast(arr, self.C.POINTER(self.C.c_void_p))
+
+    # ------------------------------------------------------------------ steps
     def forward_from_shards(self, x_rows: torch.Tensor, M: int) -> torch.Tensor:
         """Like ``forward``, but every rank passes only the rows ``owned_rows(M)`` of the activations (e.g. the
-        part of the batch it uploaded itself); the rows are replicated to all ranks through the switch
-        (``multimem.st``) inside this call.  ``exchange="switch"`` only."""
-        if self.exchange != "switch":
-            raise RuntimeError("forward_from_shards needs exchange='switch'")
-        import torch.distributed._symmetric_memory as symm_mem
+        part of the batch it uploaded itself); the rows are replicated to all ranks over NVLink inside this call
+        (one kernel: barrier, peer stores or ``multimem.st``, barrier)."""
         from . import _lib
         if self.x_full is None:
-            self.x_full = symm_mem.empty((self.tp * self.tok_per_owner, self.H), dtype=self.dtype, device=self.out.device)
-            self.h_x = symm_mem.rendezvous(self.x_full, self.group)
-            self.mc_x = int(getattr(self.h_x, "multicast_ptr", 0) or 0)
-            if not self.mc_x:
-                raise RuntimeError("no switch-replicated mapping for the activations")
+            self.x_full = self._symm.empty((self.tp * self.tok_per_owner, self.H), dtype=self.dtype, device=self.device)
+            self.h_x = self._symm.rendezvous(self.x_full, self.group)
+            self.x_ptrs = [int(p) for p in self.h_x.buffer_ptrs]
+            self.mc_x = int(getattr(self.h_x, "multicast_ptr", 0) or 0) if self.out_multicast else 0
         if M > self.max_tokens:
             raise ValueError(f"{M} tokens exceed the {self.max_tokens} this instance was built for")
         lo, hi = self.owned_rows(M)
         if x_rows.shape != (hi - lo, self.H) or not x_rows.is_contiguous():
             raise ValueError(f"rank {self.rank} must pass its rows [{lo}, {hi}) as a contiguous [{hi - lo}, {self.H}] tensor")
-        mo = block_rows(M, self.tp)
-        self.epoch += 1
+        off = self.rank * block_rows(M, self.tp) * self.row_bytes
+        self.epoch_x += 1
         # every rank launches, also one whose block is empty (M much smaller than tp * 16): the kernel's two
         # barriers are part of the protocol
         src = x_rows.data_ptr() if hi > lo else self.x_full.data_ptr()
-        rc = self.L.sfb200_tp_allgather_switch(src, self.mc_x + self.rank * mo * self.row_bytes, hi - lo, self.H,
-                                               self.C.cast(self.peer_flags, self.C.POINTER(self.C.c_void_p)),
-                                               self.tp, self.rank, self.epoch, self.ops._stream())
-        _lib.check("sfb200_tp_allgather_switch", rc)
+        peer_dst = self._VP(*[self.x_ptrs[d] + off if d < self.tp else None for d in range(8)])
+        rc = self.L.sfb200_tp_allgather(src, (self.mc_x + off) if self.mc_x else None, self._cast(peer_dst), hi - lo, self.H,
+                                        self._cast(self.peer_flags_x), self.tp, self.rank, self.epoch_x, self.ops._stream())
+        _lib.check("sfb200_tp_allgather", rc)
         self.kernel_launches += 1
         return self.forward(self.x_full[:M])
 
@@ -246,9 +288,9 @@ class FusedTensorParallelFFN:
         Without ``out`` the result is a VIEW of this instance's symmetric output buffer: it is valid until
         the next ``forward`` of this instance on ANY rank (peers write into it through NVLink), so consume
         it on the same stream before calling again, or pass ``out`` (a tensor of shape [M, H]) to receive a
-        private copy.  ``phase_events``: optional list that receives CUDA events bracketing the phases of
-        the step for per-phase timing (gate|up GEMM, down GEMM, then the exchange: one phase with
-        ``exchange="switch"``, barrier / reduce + all-gather / barrier with ``"scatter"``)."""
+        private copy.  ``phase_events``: optional list that receives four CUDA events bracketing three phases
+        of the step for per-phase timing: gate|up GEMM, down GEMM (of the first chunk), exchange (and the
+        remaining chunks)."""
         from . import _lib
         ops, L, C = self.ops, self.L, self.C
         M = x.shape[0]
@@ -257,10 +299,6 @@ class FusedTensorParallelFFN:
         st = ops._stream()
         dt = ops._dt(x)
         hidden = self.hidden[:M]
-        # rows per owner for THIS call: with the switch exchange a small batch pays a small exchange; the scatter
-        # path keeps the receive slots' fixed pitch
-        mo = block_rows(M, self.tp) if self.exchange == "switch" else self.tok_per_owner
-        blk = mo * self.row_bytes
 
         def mark():
             if phase_events is not None:
@@ -268,39 +306,58 @@ class FusedTensorParallelFFN:
                 e.record()
                 phase_events.append(e)
         bias = self.down_bias.data_ptr() if self.down_bias is not None else None
+        flags = self._cast(self.peer_flags)
         mark()
         ops.sparse_gemm_swiglu(x, self.gu, out=hidden)
         mark()
-        if self.exchange == "switch":
-            ops.sparse_gemm(hidden, self.dn, out=self.partial[:M])
-            mark()
-            self.epoch += 1
-            _lib.check("sfb200_tp_allreduce_switch", L.sfb200_tp_allreduce_switch(
-                self.mc_partial + self.rank * blk, self.mc_out + self.rank * blk, mo, self.H, dt, bias,
-                C.cast(self.peer_flags, C.POINTER(C.c_void_p)), self.tp, self.rank, self.epoch, st))
-            mark()
-        else:
-            VP = self._VP
-            # rank o's slot for my partial sums; rank d's output rows of my token block
-            slot = self.tok_per_owner * self.row_bytes
-            peer_slots = VP(*[(self.recv_ptrs[o] + self.rank * slot) if o < self.tp else None for o in range(8)])
-            peer_out = VP(*[(self.out_ptrs[d] + self.rank * blk) if d < self.tp else None for d in range(8)])
+        if self.exchange == "push":
+            # rows per owner for THIS call: a small batch pays a small exchange; slots keep their fixed pitch
+            mo = block_rows(M, self.tp)
+            slot = self.tok_per_owner * self.pbytes
+            blk = mo * self.row_bytes
+            peer_slots = self._VP(*[(self.recv_ptrs[o] + self.rank * slot) if o < self.tp else None for o in range(8)])
             _lib.check("sfb200_sparse_gemm_scatter", L.sfb200_sparse_gemm_scatter(
                 hidden.data_ptr(), hidden.stride(0), self.dn.values.data_ptr(), self.dn.meta.data_ptr(),
-                C.cast(peer_slots, C.POINTER(C.c_void_p)), self.tp, mo, M, self.H, self.Ip, dt, st))
+                self._cast(peer_slots), self.tp, mo, 1 if self.partial_f32 else 0, M, self.H, self.Ip, dt, st))
             mark()
-            self.h_recv.barrier(channel=0)            # every rank's partial sums have landed
+            self.epoch += 1
+            peer_out = self._VP(*[(self.out_ptrs[d] + self.rank * blk) if d < self.tp else None for d in range(8)])
+            mc = (self.mc_out + self.rank * blk) if self.out_multicast else None
+            _lib.check("sfb200_tp_reduce_slots", L.sfb200_tp_reduce_slots(
+                self.recv.data_ptr(), self.tok_per_owner, 1 if self.partial_f32 else 0, mc, self._cast(peer_out), mo,
+                self.H, dt, bias, flags, self.tp, self.rank, self.epoch, st))
             mark()
-            if self.switch_out_base:
-                _lib.check("sfb200_reduce_allgather_switch", L.sfb200_reduce_allgather_switch(
-                    self.recv.data_ptr(), self.tp, mo, self.H, self.switch_out_base + self.rank * blk, dt, bias, st))
-            else:
-                _lib.check("sfb200_reduce_allgather", L.sfb200_reduce_allgather(
-                    self.recv.data_ptr(), self.tp, mo, self.H, C.cast(peer_out, C.POINTER(C.c_void_p)), dt, bias, st))
+            self.kernel_launches += 3
+        else:
+            main = torch.cuda.current_stream()
+            spans = self._chunk_spans(M)
+            side = len(spans) > 1
+            for ci, (lo, hi) in enumerate(spans):
+                rows_c = hi - lo
+                if self.partial_f32:
+                    _lib.check("sfb200_sparse_gemm_f32out", L.sfb200_sparse_gemm_f32out(
+                        hidden.data_ptr() + lo * hidden.stride(0) * 2, hidden.stride(0), self.dn.values.data_ptr(),
+                        self.dn.meta.data_ptr(), self.partial.data_ptr() + lo * self.pbytes, self.H, rows_c, self.H,
+                        self.Ip, dt, None, 0, st))
+                else:
+                    ops.sparse_gemm(hidden[lo:hi], self.dn, out=self.partial[lo:hi])
+                if ci == 0:
+                    mark()
+                mo_c = block_rows(rows_c, self.tp)
+                row0 = lo + self.rank * mo_c
+                self.epoch += 1
+                if side:        # the exchange of this chunk runs beside the next chunk's GEMM
+                    ev = torch.cuda.Event()
+                    ev.record(main)
+                    self.comm_stream.wait_event(ev)
+                _lib.check("sfb200_tp_allreduce_switch", L.sfb200_tp_allreduce_switch(
+                    self.mc_partial + row0 * self.pbytes, self.mc_out + row0 * self.row_bytes, mo_c, self.H, dt,
+                    1 if self.partial_f32 else 0, bias, flags, self.tp, self.rank, self.epoch,
+                    self.comm_stream.cuda_stream if side else st))
+            if side:
+                main.wait_stream(self.comm_stream)
             mark()
-            self.h_out.barrier(channel=0)             # every rank's finished block has landed everywhere
-            mark()
-        self.kernel_launches += 3      # own kernels per step (the scatter path's two barriers are torch's)
+            self.kernel_launches += 1 + 2 * len(spans)
         res = self.out[:M]
         if out is not None:
             out.copy_(res)

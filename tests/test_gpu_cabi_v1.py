@@ -236,8 +236,8 @@ def test_select_kernel_ex_uses_content_keyed_compressed_store(tmp_path):
     db2 = str(tmp_path / "b.db").encode()
     assert L.sf_select_kernel_ex(db2, C.byref(d), C.byref(g), wd.data_ptr(), xd.data_ptr(), y.data_ptr()) == 2
     assert _row(db2.decode(), "M=4096;%")[0] == 2
-    # the timed launches wrote the caller's output: it is the GEMM of the caller's matrices
-    ref = o.gemm_ref(x[:64], oc["pruned"], dt)
+    # the timed launches wrote the caller's output; the dense candidate ran last, on the caller's weight as given
+    ref = o.gemm_ref(x[:64], w, dt)
     assert o.rel_err_metrics(o.to_f32(bits_of(y[:64]), dt), ref)["floor"] <= REL_TOL
     # a different weight of the same shape is a different key
     w2 = to_dev(seeded_weight(wm, K, dt, 43), dt)

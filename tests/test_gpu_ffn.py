@@ -31,7 +31,7 @@ def _weights(H, I, dt):
     return wg, wu, wd, [o.prune_24(w, dt)["pruned"] for w in (wg, wu, wd)]
 
 
-@pytest.mark.parametrize("bn", [0, 64, 192, 1256, 1240, 1224, 1208, 1192, 2192, 2208, 2224, 2240])
+@pytest.mark.parametrize("bn", [0, 64, 192, 1256, 1240, 1224, 1208, 1192, 2192, 2208, 2224, 2240, 5240, 5224, 5208, 5192])
 @pytest.mark.parametrize("dt", ["bf16", "f16"])
 def test_swiglu_epilogue(bn, dt):
     H, I, M = 512, 352, 300

@@ -48,7 +48,7 @@ def _run(R, K, M, dt, bn=0, sigma=0.02, wseed=1, xseed=1234, bias=False, act=Non
 
 @pytest.mark.parametrize("bn,R,K,M", [(64, 128, 64, 64), (128, 128, 128, 128), (256, 128, 256, 256),
                                       (1256, 256, 256, 256), (1240, 512, 256, 240), (1192, 256, 192, 192),
-                                      (2208, 512, 256, 208), (2240, 1024, 192, 240)])
+                                      (2208, 512, 256, 208), (2240, 1024, 192, 240), (5240, 1024, 256, 240)])
 def test_identity_activations_reproduce_pruned_weight_exactly(bn, R, K, M):
     dt = "bf16"
     w = seeded_weight(R, K, dt, 3)
@@ -61,14 +61,14 @@ def test_identity_activations_reproduce_pruned_weight_exactly(bn, R, K, M):
     assert (bits_of(y)[:n].T == o.prune_24(w, dt)["pruned"][:, :n]).all()
 
 
-@pytest.mark.parametrize("bn", [32, 64, 128, 192, 256, 1256, 1240, 1224, 1208, 1192, 2192, 2208, 2224, 2240])
+@pytest.mark.parametrize("bn", [32, 64, 128, 192, 256, 1256, 1240, 1224, 1208, 1192, 2192, 2208, 2224, 2240, 5240, 5224, 5208, 5192])
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
 def test_every_kernel_variant_ragged(bn, dt):
     y, ref = _run(392, 512, 300, dt, bn=bn)
     assert o.rel_err_metrics(y, ref)["floor"] <= REL_TOL
 
 
-@pytest.mark.parametrize("bn", [1240, 1224, 1208, 1192])
+@pytest.mark.parametrize("bn", [1240, 1224, 1208, 1192, 5240, 5192, 2240])
 def test_two_accumulator_pair_tiles_many_tiles_per_pair(bn):
     """The 256-row tiles with two accumulator sets, on a problem with more tiles than SM pairs (5 row tiles
     x 9-11 token tiles on 74 pairs would be one tile each; 24 row tiles x 9-11 gives every pair 3-4 tiles), so
@@ -98,7 +98,7 @@ def test_small_m_kernel_mistral_down_shape():
     assert o.rel_err_metrics(y, ref)["floor"] <= REL_TOL
 
 
-@pytest.mark.parametrize("bn", [128, 1256, 1240, 2208])
+@pytest.mark.parametrize("bn", [128, 1256, 1240, 2208, 5240])
 @pytest.mark.parametrize("act", [None, "relu", "silu", "gelu"])
 def test_bias_and_activation_epilogues(bn, act):
     y, ref = _run(256, 512, 200, "f16", bn=bn, bias=True, act=act)
@@ -152,13 +152,53 @@ def test_split_k_auto_dispatch_on_few_row_tiles(R, K, M):
     assert o.rel_err_metrics(o.to_f32(bits_of(y1), dt), ref)["floor"] <= REL_TOL
 
 
-@pytest.mark.parametrize("bn", [0, 1240, 2240])
+@pytest.mark.parametrize("bn", [0, 1240, 2240, 5240])
 def test_pair_kernel_l2_band_tile_order(bn):
     """Enough token tiles at K = 8192 that the prefill kernel walks them in more than one L2 band
     (12-13 token tiles, bands of 6-7), with ragged rows and tokens."""
     y, ref = _run(520, 8192, 3000, "bf16", bn=bn)
     assert y.shape == (3000, 520)
     assert o.rel_err_metrics(y, ref)["floor"] <= REL_TOL
+
+
+@pytest.mark.parametrize("order", [0, 1])
+@pytest.mark.parametrize("bn", [1256, 1240, 5240])
+def test_pair_kernel_both_tile_orders_many_bands(order, bn):
+    """Either operand as the L2-resident one (bands of token tiles / bands of row tiles), with the band budget
+    turned down to 1 MB so that a small problem walks several bands of each kind: 5 row tiles (3 at 512 rows) and
+    9-10 token tiles at K = 2048, ragged in rows and tokens."""
+    from sparseflow_b200 import _lib
+    L = _lib.lib()
+    try:
+        assert L.sfb200_debug_pair_tuning(1, order) == 0
+        y, ref = _run(1160, 2048, 2300, "bf16", bn=bn, bias=True)
+    finally:
+        assert L.sfb200_debug_pair_tuning(40, -1) == 0
+    assert y.shape == (2300, 1160)
+    assert o.rel_err_metrics(y, ref)["floor"] <= REL_TOL
+
+
+@pytest.mark.parametrize("bn", [0, 1256, 1240, 5240])
+@pytest.mark.parametrize("M", [40, 1000])
+def test_fp32_output_epilogue(bn, M):
+    """sfb200_sparse_gemm_f32out: the fp32 accumulators (+ bias) stored unrounded, for partial sums that are added
+    before they are rounded.  Against the fp32 oracle the only difference left is summation order."""
+    from sparseflow_b200 import _lib
+    dt, R, K = "bf16", 1160, 1024 + 64
+    w, x = seeded_weight(R, K, dt, 8), seeded_act(M, K, dt, 9)
+    b = seeded_act(1, R, dt, 10)[0]
+    cw = ops.compress_weight(to_dev(w, dt))
+    xd, bd = to_dev(x, dt), to_dev(b, dt)
+    y = torch.full((M, R), float("nan"), device="cuda", dtype=torch.float32)
+    ops.force_token_tile(bn)
+    rc = _lib.lib().sfb200_sparse_gemm_f32out(xd.data_ptr(), K, cw.values.data_ptr(), cw.meta.data_ptr(), y.data_ptr(), R,
+                                              M, R, K, ops.BF16, bd.data_ptr(), 0, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0 and ops.device_status() == 0
+    ref = o.gemm_ref(x, o.prune_24(w, dt)["pruned"], dt) + o.to_f32(b, dt)[None, :]
+    got = y.cpu().numpy()
+    assert np.isfinite(got).all()
+    m = o.rel_err_metrics(got, ref)
+    assert m["chain"] <= 1e-5 and m["floor"] <= 1e-3, m      # relative to the rms / to max(|ref|, 1e-2 rms)
 
 
 def test_config1_fp16_m512_k4096_n4096():
