@@ -57,13 +57,15 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama7b_ffn", choices=sorted(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=0, help="override the token count")
-    ap.add_argument("--tp", default="push", choices=["push", "switch", "nccl"],
+    ap.add_argument("--tp", default="auto", choices=["auto", "push", "pipeline", "switch", "nccl"],
                     help="N > 1: reduce-scatter by peer stores in the down GEMM's epilogue + one reduce/all-gather kernel "
-                         "(push), the exchange pulled through NVSwitch in one kernel (switch), or NCCL all-reduce (nccl)")
+                         "(push); the same movement as one light kernel per token chunk on a side stream beside the next "
+                         "chunk's GEMMs (pipeline); the exchange pulled through NVSwitch (switch); NCCL all-reduce (nccl); "
+                         "auto = push (the fastest of the four at 2 and 4 ranks with fp32 partial sums)")
     ap.add_argument("--tp-partial", default="fp32", choices=["fp32", "16bit"],
                     help="N > 1, push / switch: type of the per-rank partial sums that are exchanged (16bit halves the bytes of "
                          "the reduction but rounds every partial; see FusedTensorParallelFFN)")
-    ap.add_argument("--tp-chunks", type=int, default=1, help="N > 1, switch: token chunks of the down GEMM / exchange pipeline")
+    ap.add_argument("--tp-chunks", type=int, default=0, help="N > 1, pipeline / switch: token chunks (0 = 2 for pipeline, 1 for switch)")
     ap.add_argument("--tp-phases", action="store_true", help="N > 1: print per-phase device times to stderr")
     ap.add_argument("--chunks", type=int, default=1, help="token chunks for all-reduce overlap (N > 1, --tp nccl)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -542,14 +544,21 @@ def main():
 
     exchange = "none (single GPU)"
     ffn = None
-    if world > 1 and args.tp in ("push", "switch"):
+    if world > 1 and args.tp == "auto":
+        args.tp = "push"
+    if world > 1 and args.tp in ("push", "pipeline", "switch"):
         try:
+            chunks = args.tp_chunks or (2 if args.tp == "pipeline" else 1)
             ffn = parallel.FusedTensorParallelFFN(wg, wu, wd, max_tokens=M, partial_dtype=args.tp_partial,
-                                                  chunks=args.tp_chunks, exchange=args.tp)
+                                                  chunks=chunks, exchange=args.tp)
             exchange = (f"{args.tp_partial} partial sums; per token chunk ({len(ffn._chunk_spans(M))} chunks, exchange of chunk c "
                         "beside the down GEMM of chunk c+1) one kernel per rank: barrier, in-switch reduction "
                         "(multimem.ld_reduce), multimem.st of the finished block, barrier"
                         if ffn.exchange == "switch" else
+                        f"{args.tp_partial} partial sums; {len(ffn._chunk_spans(M))} token chunks, per chunk one light kernel per rank on "
+                        "a side stream beside the next chunk's GEMMs: peer stores of the partial blocks to their owners, barrier, "
+                        "sum of the receive slots, peer stores of the finished block to every rank, barrier"
+                        if ffn.exchange == "pipeline" else
                         f"{args.tp_partial} partial sums; reduce-scatter by peer stores in the down GEMM's epilogue, then one kernel "
                         "per rank: barrier, sum of the receive slots, peer stores of the finished block to every rank, barrier")
         except Exception as exc:      # symmetric memory unavailable on this box: NCCL path

@@ -200,6 +200,18 @@ SFB200_API int sfb200_tp_reduce_slots(const void* slots, int slot_rows, int slot
                                       void* const* peer_out_blocks, int rows, int cols, int dtype, const void* bias,
                                       void* const* peer_flags, int tp, int rank, unsigned epoch, void* stream);
 /*
+ * The whole exchange of one token chunk in ONE launch, for a GEMM that wrote its partial sums LOCALLY
+ * (sfb200_sparse_gemm / sfb200_sparse_gemm_f32out into partial_chunk): push phase -- owner block o of the chunk
+ * ([tp][block_rows, cols], valid_rows[o] live rows) is copied to peer_slots[o], the slot rank o keeps for this rank --
+ * then sfb200_tp_reduce_slots on this rank's own slots.  light = 1 launches a 128-thread form that fits beside a GEMM
+ * CTA on every SM, so that on a side stream the exchange of chunk c runs while the GEMMs of chunk c + 1 do.
+ */
+SFB200_API int sfb200_tp_push_reduce(const void* partial_chunk, int block_rows, const int* valid_rows,
+                                     void* const* peer_slots, const void* slots, int slot_rows, int slots_f32,
+                                     void* const* peer_out_blocks, int rows, int cols, int dtype, const void* bias,
+                                     void* const* peer_flags, int tp, int rank, unsigned epoch, int light,
+                                     void* stream);
+/*
  * The same exchange pulled through NVSwitch instead: every rank has written its partial output (sfb200_sparse_gemm or
  * sfb200_sparse_gemm_f32out) into its own copy of a symmetric buffer that has a switch-replicated ("multicast")
  * mapping; this rank's token block is summed across ranks inside the switch (multimem.ld_reduce) and the finished

@@ -404,6 +404,25 @@ int sfb200_sparse_gemm_f32out(const void* x, int ldx, const void* values, const 
   return launch_sparse_gemm(a, static_cast<cudaStream_t>(stream));
 }
 
+int sfb200_tp_push_reduce(const void* partial_chunk, int block_rows, const int* valid_rows, void* const* peer_slots,
+                          const void* slots, int slot_rows, int slots_f32, void* const* peer_out_blocks, int rows, int cols,
+                          int dtype, const void* bias, void* const* peer_flags, int tp, int rank, unsigned epoch, int light,
+                          void* stream) {
+  int err = kOk;
+  DeviceState* s = device_state(&err);
+  if (!s) return err;
+  if (!partial_chunk || !valid_rows || !peer_slots || tp < 2 || tp > 8) return kErrInvalid;
+  Range r("sfb200.tp_push_reduce");
+  ExchangePush push = {};
+  push.src = partial_chunk;
+  push.peer_slots = peer_slots;
+  push.block_rows = block_rows;
+  for (int o = 0; o < tp; ++o) push.valid_rows[o] = valid_rows[o];
+  push.light = light;
+  return launch_exchange(3, slots, nullptr, peer_out_blocks, rows, cols, slot_rows, slots_f32, dtype, bias, peer_flags, tp,
+                         rank, epoch, s->status, static_cast<cudaStream_t>(stream), &push);
+}
+
 int sfb200_tp_allreduce_switch(const void* mc_partial_block, void* mc_out_block, int rows, int cols, int dtype,
                                int partial_f32, const void* bias, void* const* peer_flags, int tp, int rank,
                                unsigned epoch, void* stream) {

@@ -97,9 +97,17 @@ int plan_sparse_gemm(int m_tok, int n_out, int K, int epi, int num_sms);
 // symmetric memory); epoch: 1, 2, 3, ... one per launch on that flag array, the same on every rank.  Bounded waits; on
 // a timeout the status word receives (2 << 8) | phase.
 constexpr int kSwitchFlagWords = 2 * 148 * 8;
+// Optional first phase of mode 3: the reduce-scatter as a copy, for a GEMM that wrote its partial sums locally.
+struct ExchangePush {
+  const void* src;              // local partial sums of this token chunk, owner blocks block_rows apart ([tp][block_rows, cols])
+  void* const* peer_slots;      // HOST array: peer_slots[o] = where rank o keeps this rank's block (same type as the slots)
+  int block_rows;
+  int valid_rows[8];            // live rows of owner block o (0 .. block_rows)
+  int light;                    // 1: 128-thread form that fits beside a GEMM CTA on an SM (for overlap on a side stream)
+};
 int launch_exchange(int mode, const void* src, void* mc_dst, void* const* peer_dst, int rows, int cols, int slot_rows,
                     int slots_f32, int fmt, const void* bias, void* const* peer_flags, int tp, int rank, unsigned epoch,
-                    int* status, cudaStream_t stream);
+                    int* status, cudaStream_t stream, const ExchangePush* push = nullptr);
 
 // Split-K variant of the single-CTA kernel: a cluster of `split` (2 or 4) CTAs shares one output tile,
 // each streaming a slice of K; partial tiles are reduced through distributed shared memory.  Chosen by

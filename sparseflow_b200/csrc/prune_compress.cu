@@ -16,6 +16,13 @@
 // HBM-bound: 2 B read + 1 B values + 1/8 B metadata per weight element.  One thread owns 16
 // consecutive K elements of rows m and m+8 (two 16-byte loads per row), which is exactly one
 // 32-bit metadata word; a warp streams 1 KiB of each of its two rows.
+//
+// Selection, two groups at a time in packed 16-bit halves (the integer pipe, not HBM, bounded the earlier
+// one-group-at-a-time forms: pairwise ranking ~95 instructions per group, 34 % of HBM; a key-sorting network of
+// five comparators ~50, 59 %): the magnitudes m_i of element i of both groups sit in the two halves of one word,
+// a single subtraction per pair (i, j) decides "j beats i" for both groups (bit 15 of each half of
+// (m_j | 0x8000) - m_i, no borrow crosses the halves), the six decision bits index a 64-entry table in shared
+// memory that returns the kept pair as a metadata nibble and as the byte selector that gathers the two kept values.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -24,7 +31,6 @@
 namespace sfb200 {
 namespace {
 
-constexpr uint32_t kPadNibble = 0x4;
 constexpr uint32_t kPadMeta16 = 0x4444;
 // nibble (idx0 | idx1<<2) -> reference code byte
 constexpr unsigned long long kRefCodeLut = (9ull << 16) | (4ull << 32) | (8ull << 48) |
@@ -36,34 +42,71 @@ struct GroupOut {
   uint32_t lo, hi;  // pruned group
 };
 
-// lo = (e0, e1), hi = (e2, e3) as 16-bit patterns; nan_clamp = inf pattern + 1.
-// Key = (min(|w| pattern, nan_clamp) << 2) | tie bits, unique within the group, so the two kept
-// elements are the two largest keys and their positions are the keys' low two bits.  A five
-// comparator network finds them: (a,b) = sort(k0,k1), (c,d) = sort(k2,k3); largest = max(b,d),
-// second = max(min(b,d), max(a,c)).
-template <int TIE>
-__device__ __forceinline__ GroupOut select_group(uint32_t lo, uint32_t hi, uint32_t nan_clamp) {
-  uint32_t k0 = min(lo & 0x7FFFu, nan_clamp), k1 = min((lo >> 16) & 0x7FFFu, nan_clamp);
-  uint32_t k2 = min(hi & 0x7FFFu, nan_clamp), k3 = min((hi >> 16) & 0x7FFFu, nan_clamp);
-  if (TIE == kTieHigh) {
-    k0 = k0 * 4 + 0; k1 = k1 * 4 + 1; k2 = k2 * 4 + 2; k3 = k3 * 4 + 3;
-  } else {
-    k0 = k0 * 4 + 3; k1 = k1 * 4 + 2; k2 = k2 * 4 + 1; k3 = k3 * 4 + 0;
+// Table: decision bits (b01, b02, b03, b12, b13, b23) at bit 0..5, b_ij = "element j beats element i" (i < j)
+// -> byte selector of the kept pair in bits [0, 16) (bytes 2*i0, 2*i0+1, 2*i1, 2*i1+1 of the group's two words)
+// and the nibble idx0 | idx1 << 2 in bits [16, 20).  An element is kept when at most one other element beats it.
+struct SelectLut {
+  uint32_t e[64];
+};
+constexpr SelectLut make_select_lut() {
+  SelectLut t{};
+  for (int p = 0; p < 64; ++p) {
+    const int b01 = p & 1, b02 = (p >> 1) & 1, b03 = (p >> 2) & 1, b12 = (p >> 3) & 1, b13 = (p >> 4) & 1, b23 = (p >> 5) & 1;
+    const int beaten[4] = {b01 + b02 + b03, (1 - b01) + b12 + b13, (1 - b02) + (1 - b12) + b23,
+                           (1 - b03) + (1 - b13) + (1 - b23)};
+    int i0 = -1, i1 = -1;
+    for (int i = 0; i < 4; ++i)
+      if (beaten[i] <= 1) {
+        if (i0 < 0) i0 = i;
+        else if (i1 < 0) i1 = i;
+      }
+    if (i1 < 0) { i0 = 0; i1 = 1; }   // intransitive patterns: cannot come out of a total order
+    const uint32_t sel = static_cast<uint32_t>((2 * i0) | ((2 * i0 + 1) << 4) | ((2 * i1) << 8) | ((2 * i1 + 1) << 12));
+    t.e[p] = sel | (static_cast<uint32_t>(i0 | (i1 << 2)) << 16);
   }
-  const uint32_t a = min(k0, k1), b = max(k0, k1), c = min(k2, k3), d = max(k2, k3);
-  const uint32_t first = max(b, d);
-  const uint32_t second = max(min(b, d), max(a, c));
-  uint32_t pa = first & 3u, pb = second & 3u;
-  if (TIE == kTieLow) { pa = 3u - pa; pb = 3u - pb; }
-  const uint32_t i0 = min(pa, pb), i1 = max(pa, pb);
+  return t;
+}
+__device__ const SelectLut kSelectLut = make_select_lut();
+
+__device__ __forceinline__ uint32_t min_u16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("min.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// Two groups at once: (lo0, hi0) and (lo1, hi1), each lo = (e0, e1), hi = (e2, e3) as 16-bit patterns.
+// clamp2 = (inf pattern + 1) in both halves: every NaN becomes the same largest magnitude, so NaNs tie.
+// TIE high: j beats i (i < j) iff m_j >= m_i;  TIE low: iff m_j > m_i.  Returns the two table entries.
+template <int TIE>
+__device__ __forceinline__ void select_pair(uint32_t lo0, uint32_t hi0, uint32_t lo1, uint32_t hi1, uint32_t clamp2,
+                                            const uint32_t* lut, uint32_t& e0, uint32_t& e1) {
+  // element i of both groups side by side
+  const uint32_t m0 = min_u16x2(__byte_perm(lo0, lo1, 0x5410) & 0x7FFF7FFFu, clamp2);
+  const uint32_t m1 = min_u16x2(__byte_perm(lo0, lo1, 0x7632) & 0x7FFF7FFFu, clamp2);
+  const uint32_t m2 = min_u16x2(__byte_perm(hi0, hi1, 0x5410) & 0x7FFF7FFFu, clamp2);
+  const uint32_t m3 = min_u16x2(__byte_perm(hi0, hi1, 0x7632) & 0x7FFF7FFFu, clamp2);
+  // bit 15 of each half of (m_j | 0x8000) - m_i (- 1 for "strictly greater") = "j beats i"; magnitudes are below
+  // 0x8000, so no half borrows from the other
+  constexpr uint32_t kBias = (TIE == kTieHigh) ? 0x80008000u : 0x7FFF7FFFu;
+  const uint32_t q1 = m1 + kBias, q2 = m2 + kBias, q3 = m3 + kBias;
+  const uint32_t d01 = q1 - m0, d02 = q2 - m0, d03 = q3 - m0, d12 = q2 - m1, d13 = q3 - m1, d23 = q3 - m2;
+  const uint32_t idx = ((d01 >> 15) & 0x00010001u) | ((d02 >> 14) & 0x00020002u) | ((d03 >> 13) & 0x00040004u) |
+                       ((d12 >> 12) & 0x00080008u) | ((d13 >> 11) & 0x00100010u) | ((d23 >> 10) & 0x00200020u);
+  e0 = lut[idx & 0x3Fu];
+  e1 = lut[idx >> 16];
+}
+
+__device__ __forceinline__ GroupOut finish_group(uint32_t lo, uint32_t hi, uint32_t entry, bool want_pruned) {
   GroupOut o;
-  o.nib = i0 | (i1 << 2);
-  // byte selectors (2*i, 2*i+1) for both kept elements
-  const uint32_t sel = (i0 * 0x22u + 0x10u) | ((i1 * 0x22u + 0x10u) << 8);
-  o.vals = __byte_perm(lo, hi, sel);
-  const uint32_t mask = (1u << i0) | (1u << i1);
-  o.lo = lo & ((mask & 1 ? 0xFFFFu : 0u) | (mask & 2 ? 0xFFFF0000u : 0u));
-  o.hi = hi & ((mask & 4 ? 0xFFFFu : 0u) | (mask & 8 ? 0xFFFF0000u : 0u));
+  o.vals = __byte_perm(lo, hi, entry);      // the selector is the entry's low 16 bits
+  o.nib = entry >> 16;
+  o.lo = o.hi = 0;
+  if (want_pruned) {
+    const uint32_t i0 = o.nib & 3u, i1 = o.nib >> 2;
+    const uint32_t mask = (1u << i0) | (1u << i1);
+    o.lo = lo & ((mask & 1 ? 0xFFFFu : 0u) | (mask & 2 ? 0xFFFF0000u : 0u));
+    o.hi = hi & ((mask & 4 ? 0xFFFFu : 0u) | (mask & 8 ? 0xFFFF0000u : 0u));
+  }
   return o;
 }
 
@@ -76,7 +119,7 @@ struct PruneParams {
   uint16_t* pruned;
   int out_rows, K, ld, interleave;
   int k_tiles128;
-  uint32_t nan_clamp;
+  uint32_t clamp2;     // (inf pattern + 1) in both 16-bit halves
 };
 
 __device__ __forceinline__ const uint16_t* src_row(const PruneParams& p, int r) {
@@ -89,19 +132,21 @@ __device__ __forceinline__ const uint16_t* src_row(const PruneParams& p, int r) 
 
 // Processes 16 elements of one row; returns the 16-bit metadata half word.
 template <int TIE>
-__device__ __forceinline__ uint32_t process_row16(const PruneParams& p, int r, int k0) {
+__device__ __forceinline__ uint32_t process_row16(const PruneParams& p, const uint32_t* lut, int r, int k0) {
   if (r >= p.out_rows || k0 >= p.K) return kPadMeta16;
   const uint4* s = reinterpret_cast<const uint4*>(src_row(p, r) + k0);
   const uint4 a = __ldg(s), b = __ldg(s + 1);
-  const GroupOut g0 = select_group<TIE>(a.x, a.y, p.nan_clamp);
-  const GroupOut g1 = select_group<TIE>(a.z, a.w, p.nan_clamp);
-  const GroupOut g2 = select_group<TIE>(b.x, b.y, p.nan_clamp);
-  const GroupOut g3 = select_group<TIE>(b.z, b.w, p.nan_clamp);
+  uint32_t e0, e1, e2, e3;
+  select_pair<TIE>(a.x, a.y, a.z, a.w, p.clamp2, lut, e0, e1);
+  select_pair<TIE>(b.x, b.y, b.z, b.w, p.clamp2, lut, e2, e3);
+  const bool want_pruned = p.pruned != nullptr;
+  const GroupOut g0 = finish_group(a.x, a.y, e0, want_pruned), g1 = finish_group(a.z, a.w, e1, want_pruned);
+  const GroupOut g2 = finish_group(b.x, b.y, e2, want_pruned), g3 = finish_group(b.z, b.w, e3, want_pruned);
   if (p.values) {
     uint4 v = make_uint4(g0.vals, g1.vals, g2.vals, g3.vals);
     *reinterpret_cast<uint4*>(p.values + static_cast<size_t>(r) * (p.K / 2) + k0 / 2) = v;
   }
-  if (p.pruned) {
+  if (want_pruned) {
     uint4* d = reinterpret_cast<uint4*>(p.pruned + static_cast<size_t>(r) * p.K + k0);
     d[0] = make_uint4(g0.lo, g0.hi, g1.lo, g1.hi);
     d[1] = make_uint4(g2.lo, g2.hi, g3.lo, g3.hi);
@@ -113,19 +158,22 @@ __device__ __forceinline__ uint32_t process_row16(const PruneParams& p, int r, i
                        static_cast<uint32_t>((kRefCodeLut >> (4 * g3.nib)) & 0xF) << 24;
     *reinterpret_cast<uint32_t*>(p.ref_codes + static_cast<size_t>(r) * (p.K / 4) + k0 / 4) = c;
   }
-  return g0.nib | (g1.nib << 4) | (g2.nib << 8) | (g3.nib << 12);
+  return (e0 >> 16) | ((e1 >> 12) & 0xF0u) | ((e2 >> 8) & 0xF00u) | ((e3 >> 4) & 0xF000u);
 }
 
 // grid: (ceil(Kpad / 512), Rpad / 16), block 256: warp w -> rows m0 = w and w + 8 of the 16-row
 // group, lane -> 16-element K slice.
 template <int TIE>
 __global__ void __launch_bounds__(256) prune_compress_kernel(const PruneParams p) {
+  __shared__ uint32_t lut[64];
+  if (threadIdx.x < 64) lut[threadIdx.x] = kSelectLut.e[threadIdx.x];
+  __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k0 = (blockIdx.x * 32 + lane) * 16;
   if (k0 >= p.k_tiles128 * 128) return;
   const int r_a = blockIdx.y * 16 + warp;
-  const uint32_t ma = process_row16<TIE>(p, r_a, k0);
-  const uint32_t mb = process_row16<TIE>(p, r_a + 8, k0);
+  const uint32_t ma = process_row16<TIE>(p, lut, r_a, k0);
+  const uint32_t mb = process_row16<TIE>(p, lut, r_a + 8, k0);
   if (p.meta) {
     const int rt = r_a >> 7, m2 = (r_a & 127) >> 4;
     const int kt = k0 >> 7, kb = (k0 & 127) >> 5, kh = (k0 & 31) >> 4;
@@ -137,13 +185,18 @@ __global__ void __launch_bounds__(256) prune_compress_kernel(const PruneParams p
 // Any K % 4 == 0: one thread per group, no tiled metadata.
 template <int TIE>
 __global__ void prune_generic_kernel(const PruneParams p) {
+  __shared__ uint32_t lut[64];
+  if (threadIdx.x < 64) lut[threadIdx.x] = kSelectLut.e[threadIdx.x];
+  __syncthreads();
   const int G = p.K / 4;
   const size_t total = static_cast<size_t>(p.out_rows) * G;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
     const int r = static_cast<int>(i / G), g = static_cast<int>(i % G);
     const uint2 v = *reinterpret_cast<const uint2*>(src_row(p, r) + 4 * g);
-    const GroupOut o = select_group<TIE>(v.x, v.y, p.nan_clamp);
+    uint32_t e0, e1;
+    select_pair<TIE>(v.x, v.y, v.x, v.y, p.clamp2, lut, e0, e1);
+    const GroupOut o = finish_group(v.x, v.y, e0, p.pruned != nullptr);
     if (p.values) *reinterpret_cast<uint32_t*>(p.values + static_cast<size_t>(r) * (p.K / 2) + 2 * g) = o.vals;
     if (p.pruned)
       *reinterpret_cast<uint2*>(p.pruned + static_cast<size_t>(r) * p.K + 4 * g) = make_uint2(o.lo, o.hi);
@@ -209,7 +262,7 @@ int launch_prune_compress(const PruneArgs& a, cudaStream_t stream) {
   p.ld = a.ld;
   p.interleave = a.interleave;
   p.k_tiles128 = (a.K + 127) / 128;
-  p.nan_clamp = (a.fmt == kF16 ? 0x7C00u : 0x7F80u) + 1;
+  p.clamp2 = ((a.fmt == kF16 ? 0x7C00u : 0x7F80u) + 1) * 0x00010001u;
   const bool vec_ok = (a.K % 16 == 0) && (a.ld % 8 == 0) &&
                       ((reinterpret_cast<uintptr_t>(a.dense) | reinterpret_cast<uintptr_t>(a.dense2) |
                         reinterpret_cast<uintptr_t>(a.values) | reinterpret_cast<uintptr_t>(a.pruned) |

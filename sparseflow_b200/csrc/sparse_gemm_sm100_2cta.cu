@@ -384,8 +384,13 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
           if (leader)   // bytes of BOTH CTAs land on this barrier
             mbar_arrive_expect_tx(bar_full + 8 * s,
                                   2 * (C::A_BYTES + C::B_BYTES + (load_e ? C::E_BYTES : 0)));
-          if (keep_x) tma_load_2d_pair(sbase + C::OFF_A + s * C::A_BYTES, &tmA, kt * (C::BK / 2), row0, full);
-          else tma_load_2d_pair_hint(sbase + C::OFF_A + s * C::A_BYTES, &tmA, kt * (C::BK / 2), row0, full, pol_keep);
+          // one copy per 128-row sub-tile
+#pragma unroll
+          for (int rs = 0; rs < C::RS; ++rs) {
+            const uint32_t dst = sbase + C::OFF_A + s * C::A_BYTES + rs * C::A_SUB_BYTES;
+            if (keep_x) tma_load_2d_pair(dst, &tmA, kt * (C::BK / 2), row0 + 128 * rs, full);
+            else tma_load_2d_pair_hint(dst, &tmA, kt * (C::BK / 2), row0 + 128 * rs, full, pol_keep);
+          }
 #pragma unroll
           for (int j = 0; j < C::B_SUBS; ++j) {
             const uint32_t dst = sbase + C::OFF_B + s * C::B_BYTES + j * C::B_SUB_BYTES;
@@ -676,7 +681,7 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
   }
   CUtensorMap tmA, tmB, tmE;
   const uint64_t kc = static_cast<uint64_t>(a.K) / 2;
-  if (!make_map_2d(&tmA, a.values, a.n_out, kc, kc * 2, C::ROWS_CTA, C::BK / 2,
+  if (!make_map_2d(&tmA, a.values, a.n_out, kc, kc * 2, 128, C::BK / 2,
                    C::BK == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, a.fmt))
     return kErrTensorMap;
   if (!make_map_2d(&tmB, a.x, a.m_tok, a.K, static_cast<uint64_t>(a.ldx) * 2, C::HALF_N, 64,
@@ -724,34 +729,33 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
 }
 
-// Tile choice.  Cost of a launch in units of "token columns of a 256-row tile at K = 4096":
-// waves x (MMA columns per tile + exposed epilogue).  The 256-row x 256-token tile drains its single
-// accumulator through registers (about 30 units exposed); 256-row tiles of 192..240 tokens have two
-// accumulators (epilogue hidden, a few units of hand-over); the 512-row kernel streams two
-// accumulators out in chunks (about 90 units) but does twice the work per tile.  Which one wins is
-// mostly a matter of wave quantisation on the 74 SM pairs (e.g. a 4096-row weight at 4096 tokens:
-// 256 tiles of 256 x 256 = 3.46 waves, 288 tiles of 256 x 240 = 3.89 waves).
+// Tile choice among the variants of dispatch_pair.
 int pick_pair_variant_impl(int n_out, int m_tok, int K, int pairs) {
+  // Cost of a launch in units of "one token column of a 256-row tile": measured on B200 a 256-row x bn-token tile
+  // costs about (bn + 156) units per unit of K (a constant part per K step -- feeding the weight tile -- plus a part
+  // per token column), 0.034 us per unit at K = 4096.  On top: the exposed part of the epilogue, per tile, which does
+  // not grow with K: about 31 units at K = 4096 for the tile with one accumulator set (256 tokens), about 6 for the
+  // tiles with two.  512-row tiles (3-stage, 128-wide K steps) cost about (2 bn + 264) per unit of K plus 40 exposed;
+  // they are offered only where they were measured to win: weight rows of a multiple of 4096 bytes (K % 4096 == 0;
+  // on K = 11008 and 14336 they run 1.4 - 1.5x slower than the 256-row tiles, cause not established) and at least
+  // 8192 rows.
   const double kscale = 4096.0 / (K > 0 ? K : 4096);
   auto waves = [&](long tiles) { return static_cast<double>((tiles + pairs - 1) / pairs); };
   const long rows256 = (n_out + 255) / 256;
-  const long t1 = rows256 * ((m_tok + 255) / 256);
-  double best_cost = waves(t1) * (256.0 + 30.0 * kscale);
-  int best = 1256;
-  {
-    const int cands[4] = {240, 224, 208, 192};
-    for (int bn : cands) {
-      const long t = rows256 * ((m_tok + bn - 1) / bn);
-      const double c = waves(t) * (bn + 8.0 * kscale);
-      if (c < best_cost * 0.99) { best_cost = c; best = 1000 + bn; }
-    }
+  double best_cost = 1e300;
+  int best = 1240;
+  const int cands[5] = {240, 256, 224, 208, 192};
+  for (int bn : cands) {
+    const long t = rows256 * ((m_tok + bn - 1) / bn);
+    const double c = waves(t) * (bn + 156.0 + (bn == 256 ? 31.0 : 6.0) * kscale);
+    if (c < best_cost * 0.995) { best_cost = c; best = 1000 + bn; }
   }
-  if (n_out >= 512) {
-    const int cands[4] = {192, 208, 224, 240};
-    for (int bn : cands) {
+  if (n_out >= 8192 && K % 4096 == 0) {
+    const int c2[4] = {240, 224, 208, 192};
+    for (int bn : c2) {
       const long t2 = static_cast<long>((n_out + 511) / 512) * ((m_tok + bn - 1) / bn);
-      const double c = waves(t2) * (2.0 * bn + 90.0 * kscale);
-      if (c < best_cost * 0.97) { best_cost = c; best = 2000 + bn; }
+      const double c = waves(t2) * (2.0 * bn + 264.0 + 40.0 * kscale);
+      if (c < best_cost * 0.98) { best_cost = c; best = 5000 + bn; }
     }
   }
   return best;

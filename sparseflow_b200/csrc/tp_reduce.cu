@@ -140,13 +140,54 @@ struct ExchangeArgs {
   uint32_t epoch;
   int* status;
   unsigned long long limit_ns;
+  // MODE 3, optional push phase before the entry barrier (the reduce-scatter as a copy, for GEMMs that wrote their
+  // partial sums locally): owner block o of push_src ([tp][push_block_units] units apart, push_valid_units[o] of them
+  // live) is copied to push_dst.p[o], the slot that rank o keeps for this rank
+  const void* push_src;
+  PeerOut push_dst;
+  size_t push_block_units;
+  unsigned push_valid_units[8];
 };
 
-template <bool BF16, int MODE>
-__global__ void __launch_bounds__(kExchangeThreads, 1) exchange_kernel(const ExchangeArgs a) {
+// LIGHT = 128 threads and at most 85 registers: fits on an SM BESIDE a GEMM CTA (320 threads, 54 K registers), so the
+// exchange of one token chunk can run while the GEMMs of the next chunk do.
+template <bool BF16, int MODE, bool LIGHT>
+__global__ void __launch_bounds__(LIGHT ? 128 : kExchangeThreads, LIGHT ? 6 : 1) exchange_kernel(const ExchangeArgs a) {
   __shared__ int failed;
   if (threadIdx.x == 0) failed = 0;
   __syncthreads();
+  if (MODE == 3 && a.push_src != nullptr) {
+    // same element <-> (CTA, thread) mapping as the reduction below: what CTA b of rank o reduces was pushed by
+    // CTA b of every rank, so the per-CTA barrier that follows is all the ordering the data needs
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    const int per_unit = a.slots_f32 ? 2 : 1;     // 16-byte pieces per output unit
+    for (int o = 0; o < a.tp; ++o) {
+      const uint4* src = static_cast<const uint4*>(a.push_src) + static_cast<size_t>(o) * a.push_block_units * per_unit;
+      uint4* dst = a.push_dst.p[o];
+      const size_t n = a.push_valid_units[o];
+      for (size_t i0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i0 < n; i0 += 4 * stride) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const size_t i = i0 + u * stride;
+          if (i < n) {
+            v[2 * u] = __ldcs(src + per_unit * i);
+            if (per_unit == 2) v[2 * u + 1] = __ldcs(src + 2 * i + 1);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const size_t i = i0 + u * stride;
+          if (i < n) {
+            dst[per_unit * i] = v[2 * u];
+            if (per_unit == 2) dst[2 * i + 1] = v[2 * u + 1];
+          }
+        }
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+  }
   // ---- every rank's source data is complete (its producer kernel precedes this one on its stream)
   if (!cta_rank_barrier(a.peers, a.local_flags, 0, a.tp, a.rank, a.epoch, a.status, 1, a.limit_ns)) failed = 1;
   __syncthreads();
@@ -161,26 +202,30 @@ __global__ void __launch_bounds__(kExchangeThreads, 1) exchange_kernel(const Exc
         const size_t i = i0 + u * stride;
         if (i >= a.vec) continue;
         if (MODE == 3) {
-          // all tp slots' loads are issued before the first add (local HBM / L2 reads)
-          uint4 x0[8], x1[8];
+          // four slots' loads are issued before their adds (local HBM / L2 reads), twice
           if (a.slots_f32) {
             const uint4* s = static_cast<const uint4*>(a.src) + 2 * i;
 #pragma unroll
-            for (int r = 0; r < 8; ++r)
-              if (r < a.tp) {
-                x0[r] = __ldcs(s + 2 * r * a.slot_units);
-                x1[r] = __ldcs(s + 2 * r * a.slot_units + 1);
-              }
+            for (int r0 = 0; r0 < 8; r0 += 4) {
+              uint4 x0[4], x1[4];
 #pragma unroll
-            for (int r = 0; r < 8; ++r)
-              if (r < a.tp) {
-                acc3[0] += __uint_as_float(x0[r].x); acc3[1] += __uint_as_float(x0[r].y);
-                acc3[2] += __uint_as_float(x0[r].z); acc3[3] += __uint_as_float(x0[r].w);
-                acc3[4] += __uint_as_float(x1[r].x); acc3[5] += __uint_as_float(x1[r].y);
-                acc3[6] += __uint_as_float(x1[r].z); acc3[7] += __uint_as_float(x1[r].w);
-              }
+              for (int r = 0; r < 4; ++r)
+                if (r0 + r < a.tp) {
+                  x0[r] = __ldcs(s + 2 * (r0 + r) * a.slot_units);
+                  x1[r] = __ldcs(s + 2 * (r0 + r) * a.slot_units + 1);
+                }
+#pragma unroll
+              for (int r = 0; r < 4; ++r)
+                if (r0 + r < a.tp) {
+                  acc3[0] += __uint_as_float(x0[r].x); acc3[1] += __uint_as_float(x0[r].y);
+                  acc3[2] += __uint_as_float(x0[r].z); acc3[3] += __uint_as_float(x0[r].w);
+                  acc3[4] += __uint_as_float(x1[r].x); acc3[5] += __uint_as_float(x1[r].y);
+                  acc3[6] += __uint_as_float(x1[r].z); acc3[7] += __uint_as_float(x1[r].w);
+                }
+            }
           } else {
             const uint4* s = static_cast<const uint4*>(a.src) + i;
+            uint4 x0[8];
 #pragma unroll
             for (int r = 0; r < 8; ++r)
               if (r < a.tp) x0[r] = __ldcs(s + r * a.slot_units);
@@ -259,7 +304,7 @@ __global__ void __launch_bounds__(kExchangeThreads, 1) exchange_kernel(const Exc
 
 int launch_exchange(int mode, const void* src, void* mc_dst, void* const* peer_dst, int rows, int cols, int slot_rows,
                     int slots_f32, int fmt, const void* bias, void* const* peer_flags, int tp, int rank, unsigned epoch,
-                    int* status, cudaStream_t stream) {
+                    int* status, cudaStream_t stream, const ExchangePush* push) {
   // rows == 0: this rank contributes no block but still takes part in the two barriers
   if (!src || !peer_flags || !status || rows < 0 || cols <= 0 || cols % 8 != 0) return kErrInvalid;
   if (!mc_dst && !peer_dst) return kErrInvalid;
@@ -269,6 +314,7 @@ int launch_exchange(int mode, const void* src, void* mc_dst, void* const* peer_d
   if (mode == 0 && bias) return kErrInvalid;
   if ((mode == 1 || mode == 2) && !mc_dst) return kErrInvalid;
   if (mode == 3 && slot_rows < rows) return kErrInvalid;
+  if (push && mode != 3) return kErrInvalid;
   ExchangeArgs a = {};
   for (int d = 0; d < 8; ++d) {
     void* q = peer_flags[d < tp ? d : 0];
@@ -293,13 +339,30 @@ int launch_exchange(int mode, const void* src, void* mc_dst, void* const* peer_d
   a.epoch = epoch;
   a.status = status;
   a.limit_ns = kPeerWaitLimitNs;
+  bool light = false;
+  if (push) {
+    if (!push->src || push->block_rows <= 0 || (reinterpret_cast<uintptr_t>(push->src) & 15)) return kErrInvalid;
+    a.push_src = push->src;
+    a.push_block_units = static_cast<size_t>(push->block_rows) * cols / 8;
+    for (int o = 0; o < 8; ++o) {
+      void* q = push->peer_slots[o < tp ? o : 0];
+      if (!q || (reinterpret_cast<uintptr_t>(q) & 15)) return kErrInvalid;
+      a.push_dst.p[o] = static_cast<uint4*>(q);
+      const int valid = o < tp ? push->valid_rows[o] : 0;
+      if (valid < 0 || valid > push->block_rows) return kErrInvalid;
+      a.push_valid_units[o] = static_cast<unsigned>(static_cast<size_t>(valid) * cols / 8);
+    }
+    light = push->light != 0;
+  }
   const bool bf = fmt == kBF16;
-#define SFB_LAUNCH_EXCHANGE(BF, MODE) exchange_kernel<BF, MODE><<<kExchangeCtas, kExchangeThreads, 0, stream>>>(a)
+#define SFB_LAUNCH_EXCHANGE(BF, MODE) exchange_kernel<BF, MODE, false><<<kExchangeCtas, kExchangeThreads, 0, stream>>>(a)
   if (mode == 0) SFB_LAUNCH_EXCHANGE(true, 0);
   else if (mode == 1 && bf) SFB_LAUNCH_EXCHANGE(true, 1);
   else if (mode == 1) SFB_LAUNCH_EXCHANGE(false, 1);
   else if (mode == 2 && bf) SFB_LAUNCH_EXCHANGE(true, 2);
   else if (mode == 2) SFB_LAUNCH_EXCHANGE(false, 2);
+  else if (light && bf) exchange_kernel<true, 3, true><<<kExchangeCtas, 128, 0, stream>>>(a);
+  else if (light) exchange_kernel<false, 3, true><<<kExchangeCtas, 128, 0, stream>>>(a);
   else if (bf) SFB_LAUNCH_EXCHANGE(true, 3);
   else SFB_LAUNCH_EXCHANGE(false, 3);
 #undef SFB_LAUNCH_EXCHANGE

@@ -1,25 +1,29 @@
-"""sparseflow_b200.nn -- same lazy, never-raising re-export scheme as the reference's
-sparseflow/nn/__init__.py:12-27."""
-from importlib import import_module
+"""sparseflow_b200.nn: the module-level surface of the reference's ``sparseflow.nn`` (its ``__init__`` exports
+``SparseFlowPolicy``, ``replace_llama_mlp_module``, the Linear and MLP classes and their ``make_*`` helpers,
+sparseflow/nn/__init__.py:12-27) plus ``SparseLinear`` and the ``replace_llama*`` helpers.
+
+Like upstream, importing the package must never fail because one submodule cannot be imported (torch missing, the CUDA
+library not built yet): each name is bound only if its module imports and defines it.
+"""
+import importlib
+
+_EXPORTS = {
+    "policy": ("SparseFlowPolicy",),
+    "surgery": ("replace_llama_mlp_module",),
+    "sparseflow_linear": ("SparseFlowLinear", "make_sparseflow_linear", "prune_24_dense_weight"),
+    "sparseflow_mlp": ("SparseFlowMLP", "make_sparseflow_mlp"),
+    "sparse_linear": ("SparseLinear",),
+    "replace_llama": ("replace_llama_mlp", "replace_llama_full", "replace_llama_attention"),
+}
 
 __all__ = []
-
-
-def _safe_export(mod: str, names: list) -> None:
+for _module, _names in _EXPORTS.items():
     try:
-        m = import_module(mod)
-        g = globals()
-        for n in names:
-            if hasattr(m, n):
-                g[n] = getattr(m, n)
-                __all__.append(n)
-    except Exception:
-        pass
-
-
-_safe_export("sparseflow_b200.nn.policy", ["SparseFlowPolicy"])
-_safe_export("sparseflow_b200.nn.surgery", ["replace_llama_mlp_module"])
-_safe_export("sparseflow_b200.nn.sparseflow_linear", ["SparseFlowLinear", "make_sparseflow_linear", "prune_24_dense_weight"])
-_safe_export("sparseflow_b200.nn.sparseflow_mlp", ["SparseFlowMLP", "make_sparseflow_mlp"])
-_safe_export("sparseflow_b200.nn.sparse_linear", ["SparseLinear"])
-_safe_export("sparseflow_b200.nn.replace_llama", ["replace_llama_mlp", "replace_llama_full", "replace_llama_attention"])
+        _m = importlib.import_module(f"{__name__}.{_module}")
+    except Exception:          # keep going: the other modules are still usable
+        continue
+    for _n in _names:
+        if hasattr(_m, _n):
+            globals()[_n] = getattr(_m, _n)
+            __all__.append(_n)
+del _module, _names

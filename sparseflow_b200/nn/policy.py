@@ -56,37 +56,32 @@ class SparseFlowPolicy:
         major, _ = torch.cuda.get_device_capability()
         return major == 10
 
-    def load_runtime_policy(self, path: str):
-        """Load min_m and max_m from a JSON policy file ({"ops": {name: {min_m, max_m}}})."""
-        import json
-        with open(path, "r") as f:
-            data = json.load(f)
+    # which pair of fields an op name of a policy file sets: first match wins, in the order upstream tests them
+    # (sparseflow/nn/policy.py:37-72): "gate"/"up" anywhere in the name, then "down", then q/k/v_proj, then any "o"
+    _FILE_RULES = (
+        (lambda n: "gate" in n or "up" in n, "gate_up"),
+        (lambda n: "down" in n, "down"),
+        (lambda n: "q_proj" in n or "k_proj" in n or "v_proj" in n, "qkv"),
+        (lambda n: "o" in n, "o"),
+    )
 
-        ops = data.get("ops", data)
-        for op, cfg in ops.items():
-            if not isinstance(cfg, dict):
+    def load_runtime_policy(self, path: str):
+        """Thresholds from a JSON policy file: ``{"ops": {<op name>: {"min_m": .., "max_m": ..}, ..}}`` (a file without
+        the ``"ops"`` level is read as that mapping itself).  Returns self."""
+        import json
+        with open(path, "r") as fh:
+            doc = json.load(fh)
+        table = doc.get("ops", doc)
+        for name, limits in table.items():
+            if not isinstance(limits, dict):
                 continue
-            op_lower = op.lower()
-            if "gate" in op_lower or "up" in op_lower:
-                if "min_m" in cfg:
-                    self.min_M_gate_up = int(cfg["min_m"])
-                if "max_m" in cfg:
-                    self.max_M_gate_up = int(cfg["max_m"])
-            elif "down" in op_lower:
-                if "min_m" in cfg:
-                    self.min_M_down = int(cfg["min_m"])
-                if "max_m" in cfg:
-                    self.max_M_down = int(cfg["max_m"])
-            elif any(k in op_lower for k in ["q_proj", "k_proj", "v_proj"]):
-                if "min_m" in cfg:
-                    self.min_M_qkv = int(cfg["min_m"])
-                if "max_m" in cfg:
-                    self.max_M_qkv = int(cfg["max_m"])
-            elif "o" in op_lower:
-                if "min_m" in cfg:
-                    self.min_M_o = int(cfg["min_m"])
-                if "max_m" in cfg:
-                    self.max_M_o = int(cfg["max_m"])
+            lowered = name.lower()
+            suffix = next((sfx for matches, sfx in self._FILE_RULES if matches(lowered)), None)
+            if suffix is None:
+                continue
+            for key, prefix in (("min_m", "min_M_"), ("max_m", "max_M_")):
+                if key in limits:
+                    setattr(self, prefix + suffix, int(limits[key]))
         return self
 
     def should_use_sparse(self, op_name: str, M: int) -> bool:

@@ -136,6 +136,13 @@ class FusedTensorParallelFFN:
     finished block into every rank's output (all-gather fused into the reduction), and returns when every rank is
     done.  Three launches per step, plain peer stores only, no multicast needed.
 
+    ``exchange="pipeline"``: the same data movement, scheduled for overlap instead of fused into the GEMM: tokens are
+    cut into ``chunks``; the down GEMM of a chunk writes its partial sums locally at full speed, and ONE light kernel
+    per chunk on a side stream (128 threads per SM, it fits beside a GEMM CTA) pushes them to the owners' slots, waits
+    for all ranks, reduces its own slots and stores the finished block to every rank -- while the main stream already
+    runs the GEMMs of the next chunk.  Pays where the pushes would otherwise make the down GEMM wait for NVLink
+    (four and more ranks).
+
     ``exchange="switch"``: the down GEMM writes this rank's partial sums into its own copy of a symmetric buffer; one
     kernel per rank sums its token block across ranks INSIDE NVSwitch (``multimem.ld_reduce``) and writes the finished
     block to every rank with ``multimem.st``.  Needs switch-replicated (multicast) symmetric memory.  ``chunks`` cuts
@@ -162,13 +169,13 @@ class FusedTensorParallelFFN:
         self.rank = dist.get_rank(self.group)
         if not 2 <= self.tp <= 8:
             raise ValueError("fused tensor-parallel FFN needs 2..8 ranks")
-        if exchange not in ("push", "switch"):
-            raise ValueError("exchange must be 'push' or 'switch'")
+        if exchange not in ("push", "pipeline", "switch"):
+            raise ValueError("exchange must be 'push', 'pipeline' or 'switch'")
         if partial_dtype not in ("fp32", "16bit", "bf16", "fp16"):
             raise ValueError("partial_dtype must be 'fp32' or '16bit'")
         self.exchange = exchange
         self.partial_f32 = partial_dtype == "fp32"
-        self.chunks = max(1, int(chunks)) if exchange == "switch" else 1
+        self.chunks = max(1, int(chunks)) if exchange != "push" else 1
         self.I, self.H = gate.shape
         g, u, d = shard_ffn_weights(gate, up, down, self.tp, self.rank)
         self.Ip = g.shape[0]
@@ -204,10 +211,14 @@ class FusedTensorParallelFFN:
             if not self.mc_out or not self.mc_partial:
                 raise RuntimeError("exchange='switch' needs switch-replicated (multicast) symmetric memory")
         else:
-            # receive slots [source rank][tok_per_owner, H]: rank s stores its partial sums of MY token block into slot s
-            self.recv = symm_mem.empty((tp, Mo, H), dtype=pdtype, device=dev)
+            # receive slots [source rank][slot_rows, H]: rank s stores its partial sums of MY token blocks into slot s
+            # (one block per token chunk, one after the other; 16 spare rows per possible chunk for rounding)
+            self.slot_rows = Mo + 16 * 8
+            self.recv = symm_mem.empty((tp, self.slot_rows, H), dtype=pdtype, device=dev)
             self.h_recv = symm_mem.rendezvous(self.recv, self.group)
             self.recv_ptrs = ptrs(self.h_recv)
+            if exchange == "pipeline":      # the down GEMM writes its partial sums here, locally
+                self.partial = torch.empty((tp * Mo, H), dtype=pdtype, device=dev)
         # flag words: one array for the exchange kernels (which may run on the side stream), one for the all-gather of
         # the activations (main stream); each has its own epoch counter
         nflag = self.L.sfb200_tp_flag_words()
@@ -313,7 +324,7 @@ class FusedTensorParallelFFN:
         if self.exchange == "push":
             # rows per owner for THIS call: a small batch pays a small exchange; slots keep their fixed pitch
             mo = block_rows(M, self.tp)
-            slot = self.tok_per_owner * self.pbytes
+            slot = self.slot_rows * self.pbytes
             blk = mo * self.row_bytes
             peer_slots = self._VP(*[(self.recv_ptrs[o] + self.rank * slot) if o < self.tp else None for o in range(8)])
             _lib.check("sfb200_sparse_gemm_scatter", L.sfb200_sparse_gemm_scatter(
@@ -324,10 +335,49 @@ class FusedTensorParallelFFN:
             peer_out = self._VP(*[(self.out_ptrs[d] + self.rank * blk) if d < self.tp else None for d in range(8)])
             mc = (self.mc_out + self.rank * blk) if self.out_multicast else None
             _lib.check("sfb200_tp_reduce_slots", L.sfb200_tp_reduce_slots(
-                self.recv.data_ptr(), self.tok_per_owner, 1 if self.partial_f32 else 0, mc, self._cast(peer_out), mo,
+                self.recv.data_ptr(), self.slot_rows, 1 if self.partial_f32 else 0, mc, self._cast(peer_out), mo,
                 self.H, dt, bias, flags, self.tp, self.rank, self.epoch, st))
             mark()
             self.kernel_launches += 3
+        elif self.exchange == "pipeline":
+            main = torch.cuda.current_stream()
+            spans = self._chunk_spans(M)
+            side = len(spans) > 1
+            f32 = 1 if self.partial_f32 else 0
+            slot = self.slot_rows * self.pbytes
+            soff = 0                                   # row offset of this chunk's block inside every slot
+            for ci, (lo, hi) in enumerate(spans):
+                rows_c = hi - lo
+                if self.partial_f32:
+                    _lib.check("sfb200_sparse_gemm_f32out", L.sfb200_sparse_gemm_f32out(
+                        hidden.data_ptr() + lo * hidden.stride(0) * 2, hidden.stride(0), self.dn.values.data_ptr(),
+                        self.dn.meta.data_ptr(), self.partial.data_ptr() + lo * self.pbytes, self.H, rows_c, self.H,
+                        self.Ip, dt, None, 0, st))
+                else:
+                    ops.sparse_gemm(hidden[lo:hi], self.dn, out=self.partial[lo:hi])
+                if ci == 0:
+                    mark()
+                mo_c = block_rows(rows_c, self.tp)
+                valid = (C.c_int * 8)(*[max(0, min(mo_c, rows_c - o * mo_c)) if o < self.tp else 0 for o in range(8)])
+                peer_slots = self._VP(*[(self.recv_ptrs[o] + self.rank * slot + soff * self.pbytes) if o < self.tp else None
+                                        for o in range(8)])
+                peer_out = self._VP(*[(self.out_ptrs[d] + (lo + self.rank * mo_c) * self.row_bytes) if d < self.tp else None
+                                      for d in range(8)])
+                self.epoch += 1
+                if side:        # the exchange of this chunk runs beside the next chunk's GEMMs
+                    ev = torch.cuda.Event()
+                    ev.record(main)
+                    self.comm_stream.wait_event(ev)
+                _lib.check("sfb200_tp_push_reduce", L.sfb200_tp_push_reduce(
+                    self.partial.data_ptr() + lo * self.pbytes, mo_c, valid, self._cast(peer_slots),
+                    self.recv.data_ptr() + soff * self.pbytes, self.slot_rows, f32, self._cast(peer_out), valid[self.rank],
+                    self.H, dt, bias, flags, self.tp, self.rank, self.epoch, 1 if side else 0,
+                    self.comm_stream.cuda_stream if side else st))
+                soff += mo_c
+            if side:
+                main.wait_stream(self.comm_stream)
+            mark()
+            self.kernel_launches += 1 + 2 * len(spans)
         else:
             main = torch.cuda.current_stream()
             spans = self._chunk_spans(M)

@@ -270,7 +270,7 @@ def test_kernel_plan_per_shape():
     assert plan(512, 14336, 4096) == 1256 and plan(512, 22016, 4096, 1) == 1256
     assert plan(256, 14336, 4096) == 256 and plan(512, 11008, 4096) == 192 and plan(512, 4096, 14336) == 128
     # prefill: CTA-pair kernel, 512-row tiles where they fill the waves better
-    pair = (1256, 1240, 1224, 1208, 1192, 2192, 2208, 2224, 2240)
+    pair = (1256, 1240, 1224, 1208, 1192, 2192, 2208, 2224, 2240, 5240, 5224, 5208, 5192)
     assert plan(4096, 22016, 4096, 1) in pair and plan(4096, 4096, 11008) in pair
     assert plan(1024, 4096, 4096) in pair
     assert plan(0, 4096, 4096) == 0

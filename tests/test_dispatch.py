@@ -120,3 +120,38 @@ def test_op_level_gate_with_overrides(tmp_path):
         sg.ShapeOverrides(str(tmp_path / "missing.json"), strict=True)
     with pytest.raises(ValueError):
         sg.make_overrides([{"batch": 1}])
+
+
+def test_measured_shapes_are_decided_on_their_own_measurements(tmp_path):
+    """A shape the sweep measured is decided on ITS speed-ups, not on the thresholds of its class (which the worst
+    shape of the class sets); between two measured token counts both must win; unseen shapes use the class."""
+    gate = {"min_speedup": 1.05,
+            "min_m": {"attn_proj": 2048, "ffn_gate_up": 512, "ffn_down": 512},
+            "max_m": {"attn_proj": 1 << 20, "ffn_gate_up": 1 << 20, "ffn_down": 1 << 20},
+            "decode_max_m": {"attn_proj": 32, "ffn_gate_up": 128, "ffn_down": 64},
+            "measurements": [
+                {"class": "attn_proj", "K": 8192, "N": 8192, "M": m, "speedup": s}
+                for m, s in ((16, 1.4), (128, 1.2), (512, 0.98), (1024, 1.30), (4096, 1.5))] + [
+                {"class": "attn_proj", "K": 4096, "N": 4096, "M": m, "speedup": s}
+                for m, s in ((16, 1.5), (128, 0.87), (1024, 0.94), (4096, 1.4))] + ["junk", {"K": 1}]}
+    p = tmp_path / "gate.json"
+    p.write_text(json.dumps(gate))
+    old = dispatch.GATE_FILE
+    try:
+        dispatch.reload_gate(str(p))
+        s = dispatch.should_use_sparse
+        # 8192 x 8192: wins at 1024 tokens although the class threshold says 2048
+        assert s(1024, 8192, 8192) and s(4096, 8192, 8192) and s(2000, 8192, 8192)
+        assert not s(512, 8192, 8192) and not s(300, 8192, 8192) and not s(700, 8192, 8192)    # a loss at 512 on one side
+        assert s(64, 8192, 8192) and s(1, 8192, 8192) and s(100000, 8192, 8192)                 # ends: nearest measurement
+        # 4096 x 4096: its own losses at 128 .. 1024 stand
+        assert s(16, 4096, 4096) and not s(64, 4096, 4096) and not s(1024, 4096, 4096) and s(4096, 4096, 4096)
+        assert not s(2048, 4096, 4096)                       # between a loss (1024) and a win (4096)
+        # a shape the sweep has not seen: class thresholds
+        assert dispatch.measured_decision(1024, 5120, 5120) is None
+        assert not s(1024, 5120, 5120) and s(2048, 5120, 5120) and s(32, 5120, 5120)
+        # the op-level gate reads the reloaded table too
+        from sparseflow_b200 import shape_gate as sg
+        assert sg.DEFAULT_RANGES["attn_qkv"].lo == 2048 and sg.decide("attn_qkv", 1, 2048)[0]
+    finally:
+        dispatch.reload_gate(old)

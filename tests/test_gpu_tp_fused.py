@@ -81,6 +81,12 @@ def _worker(rank, world, port, ret):
         res["push_out_arg"] = torch.equal(private, a) and private.data_ptr() != push.out.data_ptr()
         push.down_bias = bias
         res["push_bias"] = chain(push.forward(x), ref_b)
+        # ---- the same movement as a pipeline of token chunks (one light kernel per chunk on a side stream): same bits
+        for nch in (1, 3):
+            pl = F(wg, wu, wd, max_tokens=M, exchange="pipeline", chunks=nch)
+            res[f"pipeline{nch}"] = torch.equal(pl.forward(x), a) and torch.equal(pl.forward(x), a)
+            res[f"pipeline{nch}_small"] = torch.equal(pl.forward(x[:40]), a[:40])
+        res["pipeline_chunks"] = len(pl._chunk_spans(M))
         # ---- push exchange, 16-bit partial sums
         push16 = F(wg, wu, wd, max_tokens=M, partial_dtype="16bit")
         a16 = push16.forward(x).clone()
@@ -132,6 +138,7 @@ def test_tensor_parallel_ffn_two_gpus_against_oracle():
         assert r["nccl"] <= 1.5e-2 and r["nccl_bias"] <= 1.5e-2, r
         assert r["push"] <= 1e-2 and r["push_small"] <= 1e-2 and r["push_bias"] <= 1e-2, r       # fp32 partial sums
         assert r["push_repeat"] and r["push_shards"] and r["push_out_arg"], r
+        assert r["pipeline1"] and r["pipeline3"] and r["pipeline1_small"] and r["pipeline3_small"] and r["pipeline_chunks"] >= 2, r
         assert r["push16"] <= 1.5e-2, r          # (push16_vs_nccl is printed only: NCCL's summation is its own business)
         if isinstance(r["switch"], str):
             continue
