@@ -72,6 +72,16 @@ struct SparseGemmArgs {
   void* const* peer_y;
   int tp;
   int tok_per_owner;
+  // Split K in the CTA-pair kernel (few tiles, long K): caller-provided scratch for `split` fp32 partial outputs
+  // ([split][m_tok][n_out] floats) and a zeroed counter array (16 ints per 256-row x token tile).  split <= 1: unused.
+  // Filled in by launch_sparse_gemm from these three fields when the plan asks for a split variant; a caller that
+  // provides no scratch (scratch == nullptr) never gets one.
+  int lib_scratch;   // 1: launch_sparse_gemm may take the scratch from the library's per-stream slots
+  int split;
+  void* scratch;
+  size_t scratch_bytes;
+  int* counters;
+  int counter_ints;
 };
 int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream);
 // CTA-pair (cta_group::2) variant, 256-row x 256-token tiles; chosen by launch_sparse_gemm for
@@ -81,8 +91,8 @@ constexpr int kPairMinTokens = 1024;
 // Tuning hooks of the CTA-pair kernel's tile order: budget (MB) of the L2-resident operand's band (<= 0: keep),
 // and which operand is resident (-1 automatic, 0 activations, 1 weights).  Process-wide.
 void set_pair_tuning(int l2_band_mb, int force_order);
-// Variant the CTA-pair launcher picks on its own (1192..1256 or 2192..2240).
-int pick_pair_variant(int n_out, int m_tok, int K, int num_sms);
+// Variant the CTA-pair launcher picks on its own (1192..1256 or 5192..5240) and, optionally, its estimated time in us.
+int pick_pair_variant(int n_out, int m_tok, int K, int num_sms, double* cost_us = nullptr);
 // The kernel variant launch_sparse_gemm runs for a shape when nothing is forced, in the numbering of
 // SparseGemmArgs::force_bn: 8 decode kernel; 32..256 single-CTA kernel with that token tile; 1192..1256 / 2192..2240
 // CTA-pair kernel; 3000 + tile / 4000 + tile split-K cluster kernel with 2 / 4 K slices.  Host-only.

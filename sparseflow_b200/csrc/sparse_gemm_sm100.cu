@@ -20,6 +20,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "device_state.h"
 #include "kernels.h"
 #include "sm100_ptx.cuh"
 #include "tensor_map.h"
@@ -353,15 +354,16 @@ int launch_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? kOk : kErrCuda;
 }
 
-// Kernel / token-tile choice for 128 < tokens < kPairMinTokens.  In this range every candidate is bound
-// by operand traffic, not by the tensor pipe, and what decides is how many passes ("waves") the tile count
-// needs on the available SMs.  Cost of a candidate = waves x K steps x time per 64-wide K step + a fixed
-// launch/prologue/epilogue term, with the step time taken from measurements on B200:
-//   single-CTA tile of bn tokens: a step moves 9 KiB (values + metadata) + bn x 128 B (tokens); an SM
-//     sustains about 145 GB/s of operand traffic, all SMs together about 19.5 TB/s out of L2 (17 TB/s
-//     for the 256-token tile, whose ring is only four stages deep);
-//   CTA-pair tile (256 rows x 256 tokens): 275 ns per step, 6 us fixed; taken only when it wins by 3 %.
-// Returns 128 / 192 / 256 (single-CTA token tile) or 1256 (CTA-pair kernel).
+// Kernel / token-tile choice from 129 tokens up: the cheapest, by estimated time, of the single-CTA tiles and the
+// CTA-pair tiles.  Up to about a thousand tokens every candidate is bound by operand traffic, not by the tensor pipe,
+// and what decides is how many passes ("waves") the tile count needs on the available SMs (or SM pairs):
+//   single-CTA tile of bn tokens: waves x 64-wide K steps x step time + 4 us, where a step moves 9 KiB (values +
+//     metadata) + bn x 128 B (tokens), an SM sustains about 145 GB/s of operand traffic and all SMs together about
+//     19.5 TB/s out of L2 (17 TB/s for the 256-token tile, whose ring is only four stages deep);
+//   CTA-pair tiles: pick_pair_variant's estimate.
+// Measured on B200 (variants timed as CUDA graphs against this model): 22016 x 4096 at 1024 tokens 112 -> 88 us with the
+// 256 x 208 pair tile; 4096 x 11008 at 1024 tokens stays with the single-CTA 256-token tile (32 row tiles x 4 = 128 tiles
+// = one wave on 148 SMs, 59.6 us, against two waves of pair tiles, 66 us).
 int pick_mid_variant(int n_out, int m_tok, int K, int num_sms) {
   const double k64 = (K + 63) / 64;
   const long mb = (n_out + 127) / 128;
@@ -374,13 +376,12 @@ int pick_mid_variant(int n_out, int m_tok, int K, int num_sms) {
     const double active = tiles < num_sms ? static_cast<double>(tiles) : static_cast<double>(num_sms);
     const double bytes = 9216.0 + bn * 128.0;
     const double per_sm = bytes / 145e9, shared = active * bytes / (bn == 256 ? 17e12 : 19.5e12);
-    const double cost = waves * k64 * (per_sm > shared ? per_sm : shared) + 4e-6;
+    const double cost = (waves * k64 * (per_sm > shared ? per_sm : shared) + 4e-6) * 1e6;
     if (cost < best) { best = cost; pick = bn; }
   }
-  const int pairs = num_sms / 2 > 0 ? num_sms / 2 : 1;
-  const long ptiles = static_cast<long>((n_out + 255) / 256) * ((m_tok + 255) / 256);
-  const double pcost = static_cast<double>((ptiles + pairs - 1) / pairs) * k64 * 275e-9 + 6e-6;
-  if (pcost < 0.97 * best) pick = 1256;
+  double pcost = 1e30;
+  const int pv = pick_pair_variant(n_out, m_tok, K, num_sms, &pcost);
+  if (pcost < 0.97 * best) pick = pv;
   return pick;
 }
 
@@ -407,7 +408,7 @@ int plan_sparse_gemm(int m_tok, int n_out, int K, int epi, int num_sms) {
   // decode-sized token counts: bandwidth kernel on warp-level mma.sp; measured against the split-K
   // kernel it only wins at 1-2 tokens when both apply
   if (m_tok <= kSmallMMaxTokens && (split == 1 || m_tok <= 2)) return 8;
-  if (m_tok >= kPairMinTokens) return pick_pair_variant(n_out, m_tok, K, num_sms);
+  if (m_tok >= 4 * kPairMinTokens) return pick_pair_variant(n_out, m_tok, K, num_sms);   // prefill proper: pair tiles
   if (m_tok > 64 && m_tok <= 128) {
     // 65..128 tokens: one 128-token tile per row tile, two 64-token tiles, or split K.  A 128-wide stage of the
     // 128-token tile holds 50 KB and is feed-bound (~430 ns), of the 64-token tile 34 KB (~268 ns); what decides is
@@ -444,6 +445,17 @@ int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream) {
     return launch_sparse_gemm_pair(b, stream);
   }
   if (b.force_bn == 0) b.force_bn = plan_sparse_gemm(a.m_tok, a.n_out, a.K, a.epi, a.num_sms);
+  if (b.force_bn >= 60000 && b.scratch == nullptr) {
+    // split K in the pair kernel wants scratch: the library's slot of this stream, when the caller allows it and one
+    // can be had; else the best variant without it (an explicitly forced variant fails instead)
+    const int split = (b.force_bn - 60000) / 1000;
+    const size_t need = static_cast<size_t>(split) * a.m_tok * a.n_out * sizeof(float);
+    if (!(a.lib_scratch &&
+          acquire_split_scratch(stream, need, &b.scratch, &b.scratch_bytes, &b.counters, &b.counter_ints))) {
+      if (a.force_bn != 0) return kErrInvalid;
+      b.force_bn = pick_mid_variant(a.n_out, a.m_tok, a.K, a.num_sms);
+    }
+  }
   const int v = b.force_bn;
   if (v == 8) return launch_sparse_gemm_small_m(b, stream);
   if (v >= 5000) return launch_sparse_gemm_pair(b, stream);
