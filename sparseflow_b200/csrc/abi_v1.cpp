@@ -207,7 +207,6 @@ SparseFlowStatus sparseflow_sparse_gemm(SparseFlowKernel kernel, const void* A, 
   a.y = C;
   a.bias = ek >= SPARSEFLOW_EPILOGUE_BIAS ? kernel->config.epilogue.params : nullptr;
   a.status = s->status;
-  a.lib_scratch = 1;
   a.m_tok = M;
   a.n_out = N;
   a.K = K;

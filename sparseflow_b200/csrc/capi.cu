@@ -59,44 +59,6 @@ DeviceState* device_state(int* err) {
   return s;
 }
 
-bool acquire_split_scratch(cudaStream_t stream, size_t need, void** buf, size_t* bytes, int** counters,
-                           int* counter_ints) {
-  int err = kOk;
-  DeviceState* s = device_state(&err);
-  if (!s || need > DeviceState::kSplitBytes) return false;
-  std::lock_guard<std::mutex> lk(g_state_mu);
-  DeviceState::SplitSlot* slot = nullptr;
-  for (int i = 0; i < s->split_used; ++i)
-    if (s->split_slots[i].stream == stream) slot = &s->split_slots[i];
-  if (!slot) {
-    if (s->split_used >= DeviceState::kSplitSlots) return false;
-    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
-      cudaGetLastError();
-      return false;
-    }
-    void* b = nullptr;
-    int* c = nullptr;
-    const size_t cbytes = sizeof(int) * DeviceState::kSplitCounterInts;
-    if (cudaMalloc(&b, DeviceState::kSplitBytes) != cudaSuccess || cudaMalloc(&c, cbytes) != cudaSuccess ||
-        cudaMemset(c, 0, cbytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
-      cudaGetLastError();
-      if (b) cudaFree(b);
-      if (c) cudaFree(c);
-      return false;
-    }
-    slot = &s->split_slots[s->split_used++];
-    slot->stream = stream;
-    slot->buf = b;
-    slot->counters = c;
-  }
-  *buf = slot->buf;
-  *bytes = DeviceState::kSplitBytes;
-  *counters = slot->counters;
-  *counter_ints = DeviceState::kSplitCounterInts;
-  return true;
-}
-
 }  // namespace sfb200
 
 // Token-chunk plan of the host-buffer pipeline; returns the number of chunks (<= kMaxChunks),
@@ -243,7 +205,6 @@ static int run_gemm(DeviceState* s, const void* x, int ldx, const void* values, 
   a.act = act;
   a.num_sms = s->num_sms;
   a.force_bn = force_bn ? force_bn : s->force_bn;
-  a.lib_scratch = 1;
   return launch_sparse_gemm(a, st);
 }
 

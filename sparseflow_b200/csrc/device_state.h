@@ -28,28 +28,11 @@ struct DeviceState {
   cudaEvent_t ev_start = nullptr, ev_done = nullptr;
   cudaEvent_t ev_in[kMaxChunks] = {}, ev_cmp[kMaxChunks] = {};
   bool pipe_ready = false;
-  // Scratch of the split-K mode of the CTA-pair GEMM: one slot per stream that ever ran it on this device (two streams
-  // may run such GEMMs at the same time, so they cannot share partial sums or tile counters).
-  static constexpr int kSplitSlots = 8;
-  static constexpr size_t kSplitBytes = size_t{64} << 20;
-  static constexpr int kSplitCounterInts = 1 << 16;
-  struct SplitSlot {
-    cudaStream_t stream = nullptr;
-    void* buf = nullptr;
-    int* counters = nullptr;
-  } split_slots[kSplitSlots];
-  int split_used = 0;
 };
 
 // State of the current device, created on first use.  Returns nullptr and sets *err when there is
 // no usable sm_100 device.
 DeviceState* device_state(int* err);
-
-// Split-K scratch for `stream` on the current device: the slot the stream used before, else a new one (allocated and
-// zeroed here, which synchronises the device once per stream).  False when `need` bytes exceed a slot, all slots are
-// taken, the stream is being captured into a graph and has no slot yet, or the allocation fails: the caller then runs
-// a variant without split K.
-bool acquire_split_scratch(cudaStream_t stream, size_t need, void** buf, size_t* bytes, int** counters, int* counter_ints);
 
 // Status word of sfb200_ffn_forward_noalloc on the current device (it lives in the library image, not in
 // DeviceState): synchronises, reads and clears it; *word = 0 when that entry point never ran here.

@@ -72,16 +72,6 @@ struct SparseGemmArgs {
   void* const* peer_y;
   int tp;
   int tok_per_owner;
-  // Split K in the CTA-pair kernel (few tiles, long K): caller-provided scratch for `split` fp32 partial outputs
-  // ([split][m_tok][n_out] floats) and a zeroed counter array (16 ints per 256-row x token tile).  split <= 1: unused.
-  // Filled in by launch_sparse_gemm from these three fields when the plan asks for a split variant; a caller that
-  // provides no scratch (scratch == nullptr) never gets one.
-  int lib_scratch;   // 1: launch_sparse_gemm may take the scratch from the library's per-stream slots
-  int split;
-  void* scratch;
-  size_t scratch_bytes;
-  int* counters;
-  int counter_ints;
 };
 int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream);
 // CTA-pair (cta_group::2) variant, 256-row x 256-token tiles; chosen by launch_sparse_gemm for

@@ -20,7 +20,6 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-#include "device_state.h"
 #include "kernels.h"
 #include "sm100_ptx.cuh"
 #include "tensor_map.h"
@@ -445,17 +444,6 @@ int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream) {
     return launch_sparse_gemm_pair(b, stream);
   }
   if (b.force_bn == 0) b.force_bn = plan_sparse_gemm(a.m_tok, a.n_out, a.K, a.epi, a.num_sms);
-  if (b.force_bn >= 60000 && b.scratch == nullptr) {
-    // split K in the pair kernel wants scratch: the library's slot of this stream, when the caller allows it and one
-    // can be had; else the best variant without it (an explicitly forced variant fails instead)
-    const int split = (b.force_bn - 60000) / 1000;
-    const size_t need = static_cast<size_t>(split) * a.m_tok * a.n_out * sizeof(float);
-    if (!(a.lib_scratch &&
-          acquire_split_scratch(stream, need, &b.scratch, &b.scratch_bytes, &b.counters, &b.counter_ints))) {
-      if (a.force_bn != 0) return kErrInvalid;
-      b.force_bn = pick_mid_variant(a.n_out, a.m_tok, a.K, a.num_sms);
-    }
-  }
   const int v = b.force_bn;
   if (v == 8) return launch_sparse_gemm_small_m(b, stream);
   if (v >= 5000) return launch_sparse_gemm_pair(b, stream);

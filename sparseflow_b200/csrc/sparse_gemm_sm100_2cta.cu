@@ -130,12 +130,6 @@ struct PairParams {
   int band;            // tiles of the RESIDENT operand per L2 band (see tile_coords)
   int order;           // 0: activations resident (bands of token tiles); 1: weights resident (bands of row tiles)
   int out_f32;         // store epilogue: y is float [m_tok, ldy] and the fp32 results are stored unrounded
-  // Split K (store epilogue, tiles with two accumulator sets): every output tile is computed by `split` SM pairs, each
-  // over k_per_split K steps; partial tiles go to scratch[ks][m_tok][n_out] (fp32) and the warp that arrives LAST at
-  // the tile's counter adds them in slice order, applies bias / activation and stores the 16-bit output.
-  int split, k_per_split;
-  float* scratch;
-  int* counters;       // [tiles][2 CTAs][8 warps], zero before the launch; the last arriver resets its counter
 };
 
 // Tile order.  The SM pairs run in lockstep along K, so data shared by the tiles of one pass over the SMs
@@ -337,7 +331,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
   const bool leader = rank == 0;
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int num_tiles = p.num_m_blks * p.num_n_blks * p.split;      // work items: (tile, K slice), slices adjacent
+  const int num_tiles = p.num_m_blks * p.num_n_blks;
   // With BK = 64 the k loop always runs an even number of stages (a trailing stage beyond K loads
   // zero-filled operands), so metadata loads fall on every second stage without exception.
   const int k_iters = (C::BK == 128) ? (p.K + 127) / 128 : 2 * ((p.K + 127) / 128);
@@ -378,13 +372,11 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
       bool ok = true;
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
         int m_blk, n_blk;
-        tile_coords(tile / p.split, p, m_blk, n_blk);
-        const int kt_begin = (tile % p.split) * p.k_per_split;
-        const int kt_end = kt_begin + p.k_per_split < k_iters ? kt_begin + p.k_per_split : k_iters;
+        tile_coords(tile, p, m_blk, n_blk);
         const int row0 = m_blk * C::ROWS_TILE + static_cast<int>(rank) * C::ROWS_CTA;
         const int tok0 = n_blk * C::BN + static_cast<int>(rank) * C::HALF_N;
         const int e_rt0 = row0 >> 7;   // first 128-row metadata tile of this CTA
-        for (int kt = kt_begin; kt < kt_end; ++kt) {
+        for (int kt = 0; kt < k_iters; ++kt) {
           ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, err, p.status, 1);
           if (!ok) break;
           const bool load_e = (C::BK == 128) || ((kt & 1) == 0);
@@ -433,9 +425,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
         ok = mbar_wait(bar_acce + 8 * as, (use & 1u) ^ 1u, err, p.status, 3);
         if (!ok) break;
         tc_fence_after();
-        const int kt_begin = (tile % p.split) * p.k_per_split;
-        const int kt_end = kt_begin + p.k_per_split < k_iters ? kt_begin + p.k_per_split : k_iters;
-        for (int kt = kt_begin; kt < kt_end; ++kt) {
+        for (int kt = 0; kt < k_iters; ++kt) {
           ok = mbar_wait(bar_full + 8 * s, ph, err, p.status, 2);
           if (!ok) break;
           tc_fence_after();
@@ -463,7 +453,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
                                                    : make_smem_desc(a_sub, 16, 1024, kSw128);
               tc_mma_sp_f16_pair(d_base + rs * C::BN, adesc, bdesc,
                                  tmem_base + e_cols + 4 * rs + (ecol & ~1), idesc | (ecol & 1),
-                                 (kt > kt_begin || kb > 0) ? 1u : 0u);
+                                 (kt > 0 || kb > 0) ? 1u : 0u);
             }
           }
           tc_commit_pair(bar_empty + 8 * s);
@@ -486,7 +476,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
     uint32_t it = 0;
     for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++it) {
       int m_blk, n_blk;
-      tile_coords(tile / p.split, p, m_blk, n_blk);
+      tile_coords(tile, p, m_blk, n_blk);
       const uint32_t as = (C::ACC_BUFS == 2) ? (it & 1u) : 0u;
       const uint32_t use = (C::ACC_BUFS == 2) ? (it >> 1) : it;
       const uint32_t leader_acce = leader_acce0 + 8 * as;
@@ -585,62 +575,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
         if (lane == 0) mbar_arrive_remote(leader_acce);
       };
 
-      if (C::EPI == kEpiStore && kRolled && p.split > 1) {
-        // Split K: this pair holds the tile's partial sums over its K slice.  Every warp parks its part of the partial
-        // tile in scratch (one row per thread, 128 contiguous bytes per token and warp), then counts itself in at the
-        // counter of (tile, CTA, warp); the same warp index of the OTHER pairs working on this tile does the same, and
-        // whichever arrives last adds the slices in slice order (so the result does not depend on who was last),
-        // applies bias and activation, rounds and stores.  Nobody waits for anybody.
-        const int ks = tile % p.split;
-        const int row = row_w + lane;
-        const bool row_ok = row < p.n_out;
-        const size_t slice = static_cast<size_t>(p.m_tok) * p.n_out;
-        uint32_t r[16];
-#pragma unroll 1
-        for (int c = c_begin; c < 8; ++c) {
-          tmem_ld_32x32b_x16(t_acc + 16 * c, r);
-          tmem_ld_wait();
-          const int t0 = tok_w + c * 16;
-          float* dst = p.scratch + ks * slice + static_cast<size_t>(t0) * p.n_out + row;
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (row_ok && t0 + j < p.m_tok) __stcg(dst + static_cast<size_t>(j) * p.n_out, __uint_as_float(r[j]));
-        }
-        release_acc();
-        __threadfence();
-        __syncwarp();
-        int* counter = p.counters + ((tile / p.split) * 2 + static_cast<int>(rank)) * 8 + (warp - 2);
-        int arrived = 0;
-        if (lane == 0) arrived = atomicAdd(counter, 1);
-        arrived = __shfl_sync(0xffffffffu, arrived, 0);
-        if (arrived == p.split - 1) {
-          if (lane == 0) *counter = 0;          // ready for the next launch
-          __threadfence();
-          const float bias_v = (p.bias != nullptr && row_ok) ? bias_at(p.bias, row, p.fmt) : 0.f;
-#pragma unroll 1
-          for (int c = c_begin; c < 8; ++c) {
-            const int t0 = tok_w + c * 16;
-            if (t0 >= p.m_tok) break;
-            float acc16[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) acc16[j] = 0.f;
-            for (int k2 = 0; k2 < p.split; ++k2) {
-              const float* src = p.scratch + k2 * slice + static_cast<size_t>(t0) * p.n_out + row;
-#pragma unroll
-              for (int j = 0; j < 16; ++j)
-                if (row_ok && t0 + j < p.m_tok) acc16[j] += __ldcg(src + static_cast<size_t>(j) * p.n_out);
-            }
-            uint16_t* out = static_cast<uint16_t*>(p.y) + static_cast<size_t>(t0) * p.ldy + row;
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (row_ok && t0 + j < p.m_tok) {
-                const float v = act_fn(acc16[j] + bias_v, p.act);
-                out[static_cast<size_t>(j) * p.ldy] = p.fmt == 1 ? __bfloat16_as_ushort(__float2bfloat16_rn(v))
-                                                                 : __half_as_ushort(__float2half_rn(v));
-              }
-          }
-        }
-      } else if (C::EPI == kEpiStore && p.out_f32) {
+      if (C::EPI == kEpiStore && p.out_f32) {
         const bool row_ok = row_w + lane < p.n_out;
         const float bias_v = (p.bias != nullptr && row_ok) ? bias_at(p.bias, row_w + lane, p.fmt) : 0.f;
         if constexpr (kRolled) {
@@ -780,31 +715,13 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
     p.tok_per_owner = a.tok_per_owner;
   }
   p.out_f32 = a.out_f32;
-  p.split = 1;
-  p.k_per_split = (a.K + 127) / 128;
-  p.scratch = nullptr;
-  p.counters = nullptr;
-  if (a.split > 1) {
-    // split K needs a tile with two accumulator sets and 128-wide K steps, the plain store epilogue, and scratch
-    const int k_iters = (a.K + 127) / 128;
-    const size_t need = static_cast<size_t>(a.split) * a.m_tok * a.n_out * sizeof(float);
-    const size_t tiles0 = static_cast<size_t>(p.num_m_blks) * p.num_n_blks;
-    if (C::ACC_BUFS != 2 || C::BK != 128 || C::EPI != kEpiStore || a.out_f32 || a.peer_y != nullptr || a.split > k_iters ||
-        a.scratch == nullptr || a.scratch_bytes < need || a.counters == nullptr ||
-        tiles0 * 16 > static_cast<size_t>(a.counter_ints))
-      return kErrInvalid;
-    p.split = a.split;
-    p.k_per_split = (k_iters + a.split - 1) / a.split;
-    p.scratch = static_cast<float*>(a.scratch);
-    p.counters = a.counters;
-  }
   pick_order(a.n_out, a.m_tok, a.K, C::ROWS_TILE, C::BN, p.num_m_blks, p.num_n_blks, p);
   if (g_force_order >= 0) {
     p.order = g_force_order;
     p.band = p.order ? pick_band(static_cast<long>(C::ROWS_TILE * 1.125 * a.K), p.num_m_blks)
                      : pick_band(static_cast<long>(C::BN) * a.K * 2, p.num_n_blks);
   }
-  const int tiles = p.num_m_blks * p.num_n_blks * p.split;
+  const int tiles = p.num_m_blks * p.num_n_blks;
   int pairs = a.num_sms / 2;
   if (pairs > tiles) pairs = tiles;
   if (pairs < 1) pairs = 1;
@@ -856,25 +773,12 @@ int dispatch_pair(const SparseGemmArgs& a, cudaStream_t stream) {
   // 2192 / 2208 / 2224 / 2240 = 512-row tiles with that many tokens.  0 = automatic.
   int v = a.force_bn;
   if (v == 0) v = pick_pair_variant_impl(a.n_out, a.m_tok, a.K, a.num_sms / 2, nullptr);
-  if (v >= 60000) {      // 60000 + 1000 * split + token tile: split K over `split` SM pairs per tile
-    SparseGemmArgs b = a;
-    b.split = (v - 60000) / 1000;
-    b.force_bn = 1000 + v % 1000;
-    if (b.split < 2 || b.split > 8 || EPI != kEpiStore) return kErrInvalid;
-    switch (b.force_bn) {
-      case 1240: return launch_pair_cfg<PairCfg<240, 128, 4, 1, kEpiStore>>(b, stream);
-      case 1192: return launch_pair_cfg<PairCfg<192, 128, 4, 1, kEpiStore>>(b, stream);
-      case 1128: return launch_pair_cfg<PairCfg<128, 128, 4, 1, kEpiStore>>(b, stream);
-      default: return kErrInvalid;
-    }
-  }
   switch (v) {
     case 1256: return launch_pair_cfg<PairCfg<256, 128, 4, 1, EPI>>(a, stream);
     case 1240: return launch_pair_cfg<PairCfg<240, 128, 4, 1, EPI>>(a, stream);
     case 1224: return launch_pair_cfg<PairCfg<224, 128, 4, 1, EPI>>(a, stream);
     case 1208: return launch_pair_cfg<PairCfg<208, 128, 4, 1, EPI>>(a, stream);
     case 1192: return launch_pair_cfg<PairCfg<192, 128, 4, 1, EPI>>(a, stream);
-    case 1128: return launch_pair_cfg<PairCfg<128, 128, 4, 1, EPI>>(a, stream);
     case 5240: return launch_pair_cfg<PairCfg<240, 128, 3, 2, EPI>>(a, stream);
     case 5224: return launch_pair_cfg<PairCfg<224, 128, 3, 2, EPI>>(a, stream);
     case 5208: return launch_pair_cfg<PairCfg<208, 128, 3, 2, EPI>>(a, stream);
