@@ -371,7 +371,7 @@ int sfb200_sparse_gemm_scatter(const void* x, int ldx, const void* values, const
   a.peer_y = peer_slots;
   a.tp = tp;
   a.tok_per_owner = tok_per_owner;
-  if (a.force_bn < 1000 || (a.force_bn >= 3000 && a.force_bn < 5000)) a.force_bn = pick_pair_variant(N, M, K, s->num_sms);
+  if (a.force_bn < 1000 || (a.force_bn >= 3000 && a.force_bn < 5000)) a.force_bn = pick_pair_variant(N, M, K, s->num_sms, 0);
   return launch_sparse_gemm_pair(a, static_cast<cudaStream_t>(stream));
 }
 

@@ -81,8 +81,9 @@ constexpr int kPairMinTokens = 1024;
 // Tuning hooks of the CTA-pair kernel's tile order: budget (MB) of the L2-resident operand's band (<= 0: keep),
 // and which operand is resident (-1 automatic, 0 activations, 1 weights).  Process-wide.
 void set_pair_tuning(int l2_band_mb, int force_order);
-// Variant the CTA-pair launcher picks on its own (1192..1256 or 5192..5240) and, optionally, its estimated time in us.
-int pick_pair_variant(int n_out, int m_tok, int K, int num_sms, double* cost_us = nullptr);
+// Variant the CTA-pair launcher picks on its own (1192..1240 or 5192..5240; swiglu: the SiLU.mul epilogue) and,
+// optionally, its estimated time in us.
+int pick_pair_variant(int n_out, int m_tok, int K, int num_sms, int swiglu, double* cost_us = nullptr);
 // The kernel variant launch_sparse_gemm runs for a shape when nothing is forced, in the numbering of
 // SparseGemmArgs::force_bn: 8 decode kernel; 32..256 single-CTA kernel with that token tile; 1192..1256 / 2192..2240
 // CTA-pair kernel; 3000 + tile / 4000 + tile split-K cluster kernel with 2 / 4 K slices.  Host-only.

@@ -363,7 +363,7 @@ int launch_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
 // Measured on B200 (variants timed as CUDA graphs against this model): 22016 x 4096 at 1024 tokens 112 -> 88 us with the
 // 256 x 208 pair tile; 4096 x 11008 at 1024 tokens stays with the single-CTA 256-token tile (32 row tiles x 4 = 128 tiles
 // = one wave on 148 SMs, 59.6 us, against two waves of pair tiles, 66 us).
-int pick_mid_variant(int n_out, int m_tok, int K, int num_sms) {
+int pick_mid_variant(int n_out, int m_tok, int K, int num_sms, int swiglu) {
   const double k64 = (K + 63) / 64;
   const long mb = (n_out + 127) / 128;
   double best = 1e30;
@@ -379,7 +379,7 @@ int pick_mid_variant(int n_out, int m_tok, int K, int num_sms) {
     if (cost < best) { best = cost; pick = bn; }
   }
   double pcost = 1e30;
-  const int pv = pick_pair_variant(n_out, m_tok, K, num_sms, &pcost);
+  const int pv = pick_pair_variant(n_out, m_tok, K, num_sms, swiglu, &pcost);
   if (pcost < 0.97 * best) pick = pv;
   return pick;
 }
@@ -407,7 +407,7 @@ int plan_sparse_gemm(int m_tok, int n_out, int K, int epi, int num_sms) {
   // decode-sized token counts: bandwidth kernel on warp-level mma.sp; measured against the split-K
   // kernel it only wins at 1-2 tokens when both apply
   if (m_tok <= kSmallMMaxTokens && (split == 1 || m_tok <= 2)) return 8;
-  if (m_tok >= 4 * kPairMinTokens) return pick_pair_variant(n_out, m_tok, K, num_sms);   // prefill proper: pair tiles
+  if (m_tok >= 4 * kPairMinTokens) return pick_pair_variant(n_out, m_tok, K, num_sms, epi == kEpiSwiGLU);   // prefill proper: pair tiles
   if (m_tok > 64 && m_tok <= 128) {
     // 65..128 tokens: one 128-token tile per row tile, two 64-token tiles, or split K.  A 128-wide stage of the
     // 128-token tile holds 50 KB and is feed-bound (~430 ns), of the 64-token tile 34 KB (~268 ns); what decides is
@@ -425,7 +425,7 @@ int plan_sparse_gemm(int m_tok, int n_out, int K, int epi, int num_sms) {
   if (split > 1) return (split == 4 ? 4000 : 3000) + splitk_token_tile(m_tok);
   if (m_tok <= 32) return 32;
   if (m_tok <= 64) return 64;
-  return pick_mid_variant(n_out, m_tok, K, num_sms);
+  return pick_mid_variant(n_out, m_tok, K, num_sms, epi == kEpiSwiGLU);
 }
 
 int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream) {
@@ -440,7 +440,7 @@ int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream) {
     // fp32 output exists in the CTA-pair kernel's epilogue only
     if (a.epi != kEpiStore) return kErrInvalid;
     if (b.force_bn < 1000 || (b.force_bn >= 3000 && b.force_bn < 5000))
-      b.force_bn = pick_pair_variant(a.n_out, a.m_tok, a.K, a.num_sms);
+      b.force_bn = pick_pair_variant(a.n_out, a.m_tok, a.K, a.num_sms, 0);
     return launch_sparse_gemm_pair(b, stream);
   }
   if (b.force_bn == 0) b.force_bn = plan_sparse_gemm(a.m_tok, a.n_out, a.K, a.epi, a.num_sms);

@@ -19,6 +19,7 @@
 //
 // 10 warps: warp 0 = TMA producer, warp 1 = MMA issuer / tensor-memory owner, warps 2..9 = epilogue.
 // All loads are plain per-CTA TMA copies; nothing here reads another GPU's memory.
+#include <cmath>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -135,7 +136,7 @@ struct PairParams {
 // Tile order.  The SM pairs run in lockstep along K, so data shared by the tiles of one pass over the SMs
 // ("wave") is fetched from HBM once; what decides the L2 hit rate is whether the operand that the NEXT
 // wave needs again is still there.  One operand is therefore kept resident (loaded with an evict-last
-// hint) and the other is streamed: the resident operand is cut into bands of about 40 MB, and inside a band
+// hint) and the other is streamed: the resident operand is cut into bands of about 56 MB, and inside a band
 // the tiles of the streamed operand are the slow index, so that every wave touches the whole band of the
 // resident operand and only a few tiles of the streamed one.
 //   order 0: activations resident (bands of token tiles, row tile slow inside a band): gate|up-like shapes,
@@ -165,7 +166,7 @@ __device__ __forceinline__ void tile_coords(int tile, const PairParams& p, int& 
 }
 
 int g_force_order = -1;  // tuning hook: -1 automatic, 0 / 1 force the tile order
-int g_l2_band_mb = 40;   // budget of the resident operand's band (tuning hook: set_l2_band_mb)
+int g_l2_band_mb = 56;   // budget of the resident operand's band (tuning hook: set_l2_band_mb)
 
 // Tiles of the resident operand per band: `per_blk` bytes each, `count` of them in all.
 inline int pick_band(long per_blk, int count) {
@@ -228,15 +229,18 @@ struct PairCfg {
   static constexpr int D_ROW_BYTES = (EPI == kEpiSwiGLU) ? 32 : 64;
   static constexpr int D_BUF_BYTES = 16 * D_ROW_BYTES;
   static constexpr int OFF_D = OFF_E + E_STAGES * E_BYTES;
-  static constexpr int D_BYTES = 8 * 2 * D_BUF_BYTES;
+  // Epilogue warps: 4 lane quadrants x 2 (RS = 1) or x 4 (RS = 2).  The drain of a 16-column chunk is a chain of a few
+  // hundred dependent instructions, so what shortens it is more warps per scheduler, and the 512-row tiles, whose drain
+  // is not hidden behind the next tile's K loop, get sixteen (with one staging buffer each instead of two).
+  static constexpr int EPI_WARPS = (RS == 2) ? 16 : 8;
+  static constexpr int D_BUFS = (RS == 2) ? 1 : 2;
+  static constexpr int D_BYTES = EPI_WARPS * D_BUFS * D_BUF_BYTES;
   static constexpr int OFF_BAR = OFF_D + D_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-  static constexpr int EPI_WARPS = 8;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
-  // 8 epilogue warps = 4 lane quadrants x 2.  The accumulator is drained through registers in windows
-  // of 128 columns, [0, 128) and [BN - 128, BN); the second window stores only what the first does not
-  // cover, i.e. it skips its first (256 - BN) / 16 chunks.  RS = 1: the two warps of a quadrant take one
-  // window each.  RS = 2: each warp takes one accumulator and drains both windows in turn.
+  // RS = 1: the accumulator is drained in windows of 128 columns, [0, 128) and [BN - 128, BN), one per warp of a
+  // quadrant; the second window stores only what the first does not cover, i.e. it skips its first (256 - BN) / 16
+  // chunks.  RS = 2: the four warps of a quadrant take one accumulator (row set) and one half of its chunks each.
   static constexpr int COLS_PER_WARP = 128;
   static constexpr int SKIP_CHUNKS = (256 - BN) / 16;
   static constexpr int PASSES = RS;
@@ -464,12 +468,15 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
+    // ------------------------------------------------------------ epilogue (warps 2 and up, both CTAs)
     const int q = warp & 3;                 // lane quadrant
-    const int w2 = (warp - 2) >> 2;         // 0 / 1: column half (RS = 1) or accumulator (RS = 2)
-    const int acc = (C::RS == 1) ? 0 : w2;
+    const int w2 = (warp - 2) >> 2;         // RS = 1: 0 / 1 = column window; RS = 2: bit 0 = accumulator, bit 1 = chunk half
+    const int acc = (C::RS == 1) ? 0 : (w2 & 1);
     const int col0 = (C::RS == 1) ? w2 * (C::BN - 128) : 0;
-    const int c_begin = (C::RS == 1) ? w2 * C::SKIP_CHUNKS : 0;   // first chunk this warp stores
+    constexpr int kChunks = C::BN / 16, kHalf = (kChunks + 1) / 2;
+    // chunks [c_begin, c_end) of the window are this warp's to store
+    const int c_begin = (C::RS == 1) ? w2 * C::SKIP_CHUNKS : (w2 >> 1) * kHalf;
+    const int c_end = (C::RS == 1) ? 8 : ((w2 >> 1) ? kChunks : kHalf);
     const uint32_t leader_acce0 = mapa_u32(bar_acce, 0);
     const uint64_t pol_stream = l2_policy_evict_first();
     bool ok = true;
@@ -495,12 +502,15 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
       // 15 - 25 us of epilogue per tile, which bounds every tile whose K loop is shorter than that.  Where the tile has
       // TWO accumulator sets the drain is therefore a ROLLED loop over 16-column chunks (load, wait, convert, store;
       // ~150 instructions), and the accumulator is handed back after the last chunk: the MMA stream is already filling
-      // the other set.  With ONE accumulator set the accumulator has to go back as early as possible, so it is read
-      // into registers in one piece (unrolled) and handed back before conversion and stores.
-      constexpr bool kRolled = C::ACC_BUFS == 2;
+      // the other set.  The 512-row tiles (RS = 2, one accumulator set of 2 x BN columns) use the rolled loop too: their
+      // unrolled drain stalled the whole SM on instruction fetches (measured on 4096 x 11008 at 2048 tokens: 35 stall
+      // cycles per issued instruction, tensor pipe active 28 %, 197 us; rolled 77 us), the producer and the MMA issuer
+      // included.  Only the 256 x 256 tile (one accumulator set, RS = 1) reads its accumulator into registers in one
+      // piece (unrolled) and hands it back before conversion and stores.
+      constexpr bool kRolled = C::ACC_BUFS == 2 || C::RS == 2;
       const int out_cols = (C::EPI == kEpiSwiGLU) ? p.n_out / 2 : p.n_out;
       const int g = lane >> 2;
-      const uint32_t stage0 = sbase + C::OFF_D + (warp - 2) * 2 * C::D_BUF_BYTES;
+      const uint32_t stage0 = sbase + C::OFF_D + (warp - 2) * C::D_BUFS * C::D_BUF_BYTES;
       // stmatrix row address of this lane: matrix = lane / 8, row in matrix = lane % 8
       const int mt = lane >> 3, rr = lane & 7;
       const uint32_t st_off = static_cast<uint32_t>((rr + 8 * (mt >> 1)) * C::D_ROW_BYTES + 16 * (mt & 1));
@@ -522,7 +532,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
       // behind the producer's loads in the copy engine and its completion, which the staging buffer's reuse has to
       // wait for, takes longer than the chunk itself.)
       auto store_chunk16 = [&](const uint32_t* a, const uint32_t* b, int c, int t0, float b0, float b1, float b2, float b3) {
-        const uint32_t stage = stage0 + (c & 1) * C::D_BUF_BYTES;
+        const uint32_t stage = stage0 + (c & (C::D_BUFS - 1)) * C::D_BUF_BYTES;
         __syncwarp();                                 // every lane has read this buffer's previous contents
         if (C::EPI == kEpiSwiGLU) {
           // half 0 = 16 gate rows, half 1 = the 16 matching up rows: pairing is in-thread
@@ -581,7 +591,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
         if constexpr (kRolled) {
           uint32_t r[16];
 #pragma unroll 1
-          for (int c = c_begin; c < 8; ++c) {
+          for (int c = c_begin; c < c_end; ++c) {
             tmem_ld_32x32b_x16(t_acc + 16 * c, r);
             tmem_ld_wait();
             const int t0 = tok_w + c * 16;
@@ -615,15 +625,26 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
           if (row_w + g + 24 < p.n_out) b3 = bias_at(p.bias, row_w + g + 24, p.fmt);
         }
         if constexpr (kRolled) {
-          uint32_t a[8], b[8];
+          // two register sets in turn: the loads of chunk c + 1 are in flight while chunk c is converted and stored
+          uint32_t ra[8], rb[8], sa[8], sb[8];
+          auto load_chunk = [&](int c, uint32_t (&lo)[8], uint32_t (&hi)[8]) {
+            tmem_ld_16x256b_x2(t_acc + 16 * c, lo);                                          // lanes q*32 + 0..15
+            tmem_ld_16x256b_x2(t_acc + 16 * c + (static_cast<uint32_t>(16) << 16), hi);      // lanes q*32 + 16..31
+          };
+          load_chunk(c_begin, ra, rb);
 #pragma unroll 1
-          for (int c = c_begin; c < 8; ++c) {
-            tmem_ld_16x256b_x2(t_acc + 16 * c, a);                                          // lanes q*32 + 0..15
-            tmem_ld_16x256b_x2(t_acc + 16 * c + (static_cast<uint32_t>(16) << 16), b);      // lanes q*32 + 16..31
+          for (int c = c_begin; c < c_end; c += 2) {
             tmem_ld_wait();
-            store_chunk16(a, b, c, tok_w + c * 16, b0, b1, b2, b3);
+            if (c + 1 < c_end) load_chunk(c + 1, sa, sb);
+            else release_acc();                                  // last chunk is in registers
+            store_chunk16(ra, rb, c, tok_w + c * 16, b0, b1, b2, b3);
+            if (c + 1 < c_end) {
+              tmem_ld_wait();
+              if (c + 2 < c_end) load_chunk(c + 2, ra, rb);
+              else release_acc();
+              store_chunk16(sa, sb, c + 1, tok_w + (c + 1) * 16, b0, b1, b2, b3);
+            }
           }
-          release_acc();
         } else {
           // both 16-lane halves of this warp's quadrant, one window of 128 columns, in the MMA-fragment layout; one
           // wait per window; the accumulator is handed back after the LAST window's loads have landed
@@ -730,38 +751,44 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
 }
 
 // Tile choice among the variants of dispatch_pair: estimated kernel time in microseconds from measurements on B200.
-//   256-row x bn tile with two accumulator sets (12xx): a 128-wide K step costs 0.166 + 0.00106 * bn us (a constant part
-//     for the weight tile plus a part per token column; the drain is hidden behind the next tile);
-//   256 x 256 with one accumulator set (1256): its unrolled drain runs out of the instruction cache and is exposed
-//     (15-25 us per tile unless the K loop is longer than that), so it is offered only for K >= 16384, where it
-//     measured 5 % ahead of the 240-token tile (8192 x 28672 at 8192 tokens);
-//   512-row tiles (52xx: 3 stages of K = 128, one accumulator set): 0.2806 + 0.00212 * bn us per K step + 1.4 us exposed
-//     per tile; offered only where they were measured to win: at least 4096 tokens, at least 16384 rows and weight rows
-//     of a multiple of 4096 bytes (on K = 11008 and 14336 they run 1.4 - 1.5x slower than the 256-row tiles, cause
-//     not established);
+//   256-row x bn tile with two accumulator sets (12xx): a 128-wide K step costs 0.159 + 0.00102 * bn us (a constant
+//     part for the weight tile plus a part per token column; the drain is hidden behind the next tile), 10 % more when
+//     the activations are the streamed operand (tile order 1: few rows, long K -- the down projections), and 3 % more
+//     per doubling of K above 4096 (measured per step, 240-token tile: 0.404 us on 22016 x 4096, 0.43 on 57344 x 8192,
+//     0.45 - 0.47 on 4096 x 11008 / 14336, 0.48 on 8192 x 28672);
+//   512-row tiles (52xx: 3 stages of K = 128, one accumulator set of 2 x bn columns, sixteen epilogue warps): the token
+//     tile is written to shared memory once and read by two row sets, 0.27 + 0.00217 * bn us per K step whatever the
+//     order, + 4 us of exposed drain per tile with the plain store epilogue (the SiLU.mul epilogue stores half as
+//     much and measured no exposed part): they win where K is long (4096 x 11008 at 4096 tokens 161 -> 145 us,
+//     4096 x 14336 210 -> 188 us, 8192 x 28672 834 -> 735 us) and tie on the gate|up shapes of K = 4096;
+//   256 x 256 with one accumulator set (1256): its unrolled drain runs out of the instruction cache and is exposed;
+//     since the 512-row tiles got their rolled drain it is never the fastest and is kept for forcing only;
 //   launch, prologue, first fill and last drain: 8.5 us.
 // What decides in practice is the number of passes over the SM pairs.
-int pick_pair_variant_impl(int n_out, int m_tok, int K, int pairs, double* cost_us) {
+int pick_pair_variant_impl(int n_out, int m_tok, int K, int pairs, int swiglu, double* cost_us) {
   const double k128 = (K + 127) / 128;
+  const double fk = k128 > 32.0 ? 1.0 + 0.03 * std::log2(k128 / 32.0) : 1.0;
+  const bool x_streamed = static_cast<double>(n_out) * K * 1.125 < static_cast<double>(m_tok) * K * 2.0;   // as pick_order
+  const double f12 = fk * (x_streamed ? 1.10 : 1.0);
   auto waves = [&](long tiles) { return static_cast<double>((tiles + pairs - 1) / pairs); };
   const long rows256 = (n_out + 255) / 256;
   double best_cost = 1e300;
   int best = 1240;
   const int cands[4] = {240, 224, 208, 192};
   for (int bn : cands) {
-    const double c = 8.5 + waves(rows256 * ((m_tok + bn - 1) / bn)) * k128 * (0.166 + 0.00106 * bn);
-    if (c < best_cost * 0.995) { best_cost = c; best = 1000 + bn; }
+    const double c = 8.5 + waves(rows256 * ((m_tok + bn - 1) / bn)) * k128 * (0.159 + 0.00102 * bn) * f12;
+    if (c < best_cost * 0.985) { best_cost = c; best = 1000 + bn; }
   }
-  if (K >= 16384) {
-    const double c = 8.5 + waves(rows256 * ((m_tok + 255) / 256)) * (k128 * (0.166 + 0.00106 * 256) + 1.0);
-    if (c < best_cost * 0.98) { best_cost = c; best = 1256; }
-  }
-  if (m_tok >= 4096 && n_out >= 16384 && K % 4096 == 0) {
+  if (m_tok >= 1024 && n_out >= 1024) {
+    double c5 = 1e300;
+    int b5 = 0;
     for (int bn : cands) {
       const long t2 = static_cast<long>((n_out + 511) / 512) * ((m_tok + bn - 1) / bn);
-      const double c = 8.5 + waves(t2) * (k128 * (0.2806 + 0.00212 * bn) + 1.4);
-      if (c < best_cost * 0.98) { best_cost = c; best = 5000 + bn; }
+      const double crowd = t2 <= pairs ? 0.93 : 1.0;   // a single, partly filled pass: less contention for L2 (measured)
+      const double c = 8.5 + waves(t2) * (k128 * (0.27 + 0.00217 * bn) * crowd + (swiglu ? 0.0 : 4.0));
+      if (c < c5 * 0.985) { c5 = c; b5 = 5000 + bn; }
     }
+    if (c5 < best_cost * 0.98) { best_cost = c5; best = b5; }
   }
   if (cost_us) *cost_us = best_cost;
   return best;
@@ -772,7 +799,7 @@ int dispatch_pair(const SparseGemmArgs& a, cudaStream_t stream) {
   // force_bn: 1256 / 1240 / 1224 / 1208 / 1192 = 256-row tiles with that many tokens;
   // 2192 / 2208 / 2224 / 2240 = 512-row tiles with that many tokens.  0 = automatic.
   int v = a.force_bn;
-  if (v == 0) v = pick_pair_variant_impl(a.n_out, a.m_tok, a.K, a.num_sms / 2, nullptr);
+  if (v == 0) v = pick_pair_variant_impl(a.n_out, a.m_tok, a.K, a.num_sms / 2, EPI == kEpiSwiGLU, nullptr);
   switch (v) {
     case 1256: return launch_pair_cfg<PairCfg<256, 128, 4, 1, EPI>>(a, stream);
     case 1240: return launch_pair_cfg<PairCfg<240, 128, 4, 1, EPI>>(a, stream);
@@ -798,8 +825,8 @@ void set_pair_tuning(int l2_band_mb, int force_order) {
   g_force_order = force_order;
 }
 
-int pick_pair_variant(int n_out, int m_tok, int K, int num_sms, double* cost_us) {
-  return pick_pair_variant_impl(n_out, m_tok, K, num_sms / 2 > 0 ? num_sms / 2 : 1, cost_us);
+int pick_pair_variant(int n_out, int m_tok, int K, int num_sms, int swiglu, double* cost_us) {
+  return pick_pair_variant_impl(n_out, m_tok, K, num_sms / 2 > 0 ? num_sms / 2 : 1, swiglu, cost_us);
 }
 
 int launch_sparse_gemm_pair(const SparseGemmArgs& a, cudaStream_t stream) {

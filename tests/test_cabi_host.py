@@ -267,11 +267,12 @@ def test_kernel_plan_per_shape():
     assert plan(9, 22016, 4096) == 32 and plan(33, 22016, 4096) == 64 and plan(100, 11008, 4096) == 128
     assert plan(64, 22016, 4096, 1) == 64             # the SwiGLU epilogue has no split-K form
     # from 129 tokens: the cheapest of single-CTA tiles and CTA-pair tiles by estimated time (passes over the SMs)
-    assert plan(512, 14336, 4096) == 1192 and plan(512, 22016, 4096, 1) == 1192 and plan(1024, 22016, 4096, 1) == 1208
+    assert plan(512, 14336, 4096) == 1192 and plan(512, 22016, 4096, 1) == 1192 and plan(1024, 22016, 4096, 1) == 5208
     assert plan(256, 14336, 4096) == 256 and plan(512, 4096, 14336) == 128 and plan(1024, 4096, 4096) == 256
     assert plan(768, 4096, 11008) == 1192 and plan(768, 4096, 4096) == 192
-    # prefill: 256-row tiles with two accumulator sets; the 256-token tile only for very long K; 512-row tiles only for
-    # many rows, many tokens and weight rows of a multiple of 4096 bytes
-    assert plan(4096, 22016, 4096, 1) == 1240 and plan(4096, 4096, 11008) == 1240 and plan(2048, 22016, 4096, 1) == 1240
-    assert plan(8192, 57344, 8192, 1) == 5240 and plan(8192, 8192, 28672) == 1256 and plan(16384, 8192, 8192) == 1240
+    # prefill: 256-row tiles with two accumulator sets where K is short (the drain hides behind the next tile), 512-row
+    # tiles (the token tile is read by two row sets) where K is long or the passes over the SM pairs come out fewer
+    assert plan(4096, 22016, 4096, 1) == 1240 and plan(4096, 4096, 4096) == 1240 and plan(2048, 22016, 4096, 1) == 5208
+    assert plan(4096, 4096, 11008) == 5240 and plan(4096, 4096, 14336) == 5240 and plan(2048, 4096, 11008) == 5240
+    assert plan(8192, 57344, 8192, 1) == 5240 and plan(8192, 8192, 28672) == 5224 and plan(16384, 8192, 8192) == 5240
     assert plan(0, 4096, 4096) == 0
