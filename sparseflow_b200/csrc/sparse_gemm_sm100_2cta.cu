@@ -752,10 +752,10 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
 
 // Tile choice among the variants of dispatch_pair: estimated kernel time in microseconds from measurements on B200.
 //   256-row x bn tile with two accumulator sets (12xx): a 128-wide K step costs 0.159 + 0.00102 * bn us (a constant
-//     part for the weight tile plus a part per token column; the drain is hidden behind the next tile), 10 % more when
-//     the activations are the streamed operand (tile order 1: few rows, long K -- the down projections), and 3 % more
-//     per doubling of K above 4096 (measured per step, 240-token tile: 0.404 us on 22016 x 4096, 0.43 on 57344 x 8192,
-//     0.45 - 0.47 on 4096 x 11008 / 14336, 0.48 on 8192 x 28672);
+//     part for the weight tile plus a part per token column; the drain is hidden behind the next tile), 5 % more when
+//     the activations are the streamed operand (tile order 1: few rows, long K -- the down projections), and 8 % more
+//     per doubling of K above 4096, up to 12 % (measured per step, 240-token tile: 0.404 us on 22016 x 4096, 0.43 - 0.44
+//     on 57344 x 8192 and 8192 x 8192, 0.45 - 0.47 on 4096 x 11008 / 14336, 0.48 on 8192 x 28672);
 //   512-row tiles (52xx: 3 stages of K = 128, one accumulator set of 2 x bn columns, sixteen epilogue warps): the token
 //     tile is written to shared memory once and read by two row sets, 0.27 + 0.00217 * bn us per K step whatever the
 //     order, + 4 us of exposed drain per tile with the plain store epilogue (the SiLU.mul epilogue stores half as
@@ -767,9 +767,10 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
 // What decides in practice is the number of passes over the SM pairs.
 int pick_pair_variant_impl(int n_out, int m_tok, int K, int pairs, int swiglu, double* cost_us) {
   const double k128 = (K + 127) / 128;
-  const double fk = k128 > 32.0 ? 1.0 + 0.03 * std::log2(k128 / 32.0) : 1.0;
+  const double dbl = k128 > 32.0 ? std::log2(k128 / 32.0) : 0.0;
+  const double fk = 1.0 + 0.08 * (dbl < 1.5 ? dbl : 1.5);
   const bool x_streamed = static_cast<double>(n_out) * K * 1.125 < static_cast<double>(m_tok) * K * 2.0;   // as pick_order
-  const double f12 = fk * (x_streamed ? 1.10 : 1.0);
+  const double f12 = fk * (x_streamed ? 1.05 : 1.0);
   auto waves = [&](long tiles) { return static_cast<double>((tiles + pairs - 1) / pairs); };
   const long rows256 = (n_out + 255) / 256;
   double best_cost = 1e300;
