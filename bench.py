@@ -62,7 +62,7 @@ def parse_args():
                          "(push); the same movement as one light kernel per token chunk on a side stream beside the next "
                          "chunk's GEMMs (pipeline); the exchange pulled through NVSwitch (switch); NCCL all-reduce (nccl); "
                          "auto = push (the fastest of the four at 2 and 4 ranks with fp32 partial sums)")
-    ap.add_argument("--tp-partial", default="fp32", choices=["fp32", "16bit"],
+    ap.add_argument("--tp-partial", default="fp32", choices=["fp32", "fp16", "16bit"],
                     help="N > 1, push / switch: type of the per-rank partial sums that are exchanged (16bit halves the bytes of "
                          "the reduction but rounds every partial; see FusedTensorParallelFFN)")
     ap.add_argument("--tp-chunks", type=int, default=0, help="N > 1, pipeline / switch: token chunks (0 = 2 for pipeline, 1 for switch)")

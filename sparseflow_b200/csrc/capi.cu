@@ -367,7 +367,8 @@ int sfb200_sparse_gemm_scatter(const void* x, int ldx, const void* values, const
   a.act = kActNone;
   a.num_sms = s->num_sms;
   a.force_bn = s->force_bn;
-  a.out_f32 = slots_f32 ? 1 : 0;
+  if (slots_f32 < 0 || slots_f32 > 2) return kErrInvalid;
+  a.out_f32 = slots_f32;
   a.peer_y = peer_slots;
   a.tp = tp;
   a.tok_per_owner = tok_per_owner;

@@ -64,7 +64,8 @@ struct SparseGemmArgs {
   int act;
   int num_sms;
   int force_bn;           // 0 = choose by token count
-  int out_f32;            // 1: y is float [m_tok, ldy], results stored unrounded (kEpiStore, CTA-pair kernel only)
+  int out_f32;            // 1: y is float [m_tok, ldy], results stored unrounded; 2: y is fp16 whatever the operand type,
+                          // results clamped to the finite fp16 range (kEpiStore, CTA-pair kernel only)
   // Row-parallel GEMM of a tensor-parallel FFN with the reduce-scatter fused into the epilogue (CTA-pair kernel,
   // kEpiStore): token block o (tok_per_owner tokens, a multiple of 16) of this rank's partial output is stored to
   // peer_y[o] -- rank o's receive slot for this rank, [tok_per_owner, ldy], 16-bit or float per out_f32 -- instead of y.
@@ -89,7 +90,7 @@ int pick_pair_variant(int n_out, int m_tok, int K, int num_sms, int swiglu, doub
 // CTA-pair kernel; 3000 + tile / 4000 + tile split-K cluster kernel with 2 / 4 K slices.  Host-only.
 int plan_sparse_gemm(int m_tok, int n_out, int K, int epi, int num_sms);
 // The exchange step (reduction + all-gather) of the row-parallel GEMM in one launch per rank, cross-GPU ordering
-// included.  mode 3: src = LOCAL receive slots [tp][slot_rows, cols] (float or 16-bit per slots_f32) that the ranks' GEMM
+// included.  mode 3: src = LOCAL receive slots [tp][slot_rows, cols] (slots_f32 = 0: 16-bit of the output type, 1: float, 2: fp16 whatever the output type) that the ranks' GEMM
 // epilogues filled; the first `rows` rows of every slot are summed in fp32, bias added, rounded once and stored into
 // every rank's output block (peer_dst[d], plain peer stores; or mc_dst, one multimem store).  mode 1 / 2: src = this
 // rank's block inside the MULTICAST mapping of a symmetric buffer of 16-bit / float partial sums, summed inside

@@ -130,7 +130,8 @@ struct PairParams {
   void* peer_y[8];
   int band;            // tiles of the RESIDENT operand per L2 band (see tile_coords)
   int order;           // 0: activations resident (bands of token tiles); 1: weights resident (bands of row tiles)
-  int out_f32;         // store epilogue: y is float [m_tok, ldy] and the fp32 results are stored unrounded
+  int out_f32;         // store epilogue: 1 = y is float [m_tok, ldy], results stored unrounded; 2 = y is fp16 whatever
+                       // the operand type, results clamped to the finite fp16 range (partial sums on their way to a sum)
 };
 
 // Tile order.  The SM pairs run in lockstep along K, so data shared by the tiles of one pass over the SMs
@@ -541,12 +542,17 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
                             pack16(silu_mul(a[4], b[4]), silu_mul(a[5], b[5]), p.fmt),
                             pack16(silu_mul(a[6], b[6]), silu_mul(a[7], b[7]), p.fmt));
         } else {
-          auto f = [&](uint32_t v, float bias) { return act_fn(__uint_as_float(v) + bias, p.act); };
-          stmatrix_x4_trans(stage + st_off, pack16(f(a[0], b0), f(a[1], b0), p.fmt), pack16(f(a[2], b1), f(a[3], b1), p.fmt),
-                            pack16(f(a[4], b0), f(a[5], b0), p.fmt), pack16(f(a[6], b1), f(a[7], b1), p.fmt));
-          stmatrix_x4_trans(stage + st_off + 32, pack16(f(b[0], b2), f(b[1], b2), p.fmt),
-                            pack16(f(b[2], b3), f(b[3], b3), p.fmt), pack16(f(b[4], b2), f(b[5], b2), p.fmt),
-                            pack16(f(b[6], b3), f(b[7], b3), p.fmt));
+          const bool half_out = p.out_f32 == 2;
+          const int of = half_out ? 0 : p.fmt;
+          auto f = [&](uint32_t v, float bias) {
+            const float r = act_fn(__uint_as_float(v) + bias, p.act);
+            return half_out ? fminf(fmaxf(r, -65504.f), 65504.f) : r;
+          };
+          stmatrix_x4_trans(stage + st_off, pack16(f(a[0], b0), f(a[1], b0), of), pack16(f(a[2], b1), f(a[3], b1), of),
+                            pack16(f(a[4], b0), f(a[5], b0), of), pack16(f(a[6], b1), f(a[7], b1), of));
+          stmatrix_x4_trans(stage + st_off + 32, pack16(f(b[0], b2), f(b[1], b2), of),
+                            pack16(f(b[2], b3), f(b[3], b3), of), pack16(f(b[4], b2), f(b[5], b2), of),
+                            pack16(f(b[6], b3), f(b[7], b3), of));
         }
         int tl;
         uint16_t* base = static_cast<uint16_t*>(chunk_dst(t0, tl));
@@ -585,7 +591,7 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
         if (lane == 0) mbar_arrive_remote(leader_acce);
       };
 
-      if (C::EPI == kEpiStore && p.out_f32) {
+      if (C::EPI == kEpiStore && p.out_f32 == 1) {
         const bool row_ok = row_w + lane < p.n_out;
         const float bias_v = (p.bias != nullptr && row_ok) ? bias_at(p.bias, row_w + lane, p.fmt) : 0.f;
         if constexpr (kRolled) {

@@ -133,6 +133,7 @@ struct ExchangeArgs {
   size_t slot_units;      // MODE 3: distance between two source ranks' slots, in output units
   int vec_per_row;
   int slots_f32;          // MODE 3: slots hold floats
+  int slots_half;         // MODE 3: slots hold fp16 whatever the output type
   const uint16_t* bias;
   FlagPeers peers;
   uint32_t* local_flags;
@@ -231,7 +232,10 @@ __global__ void __launch_bounds__(LIGHT ? 128 : kExchangeThreads, LIGHT ? 6 : 1)
               if (r < a.tp) x0[r] = __ldcs(s + r * a.slot_units);
 #pragma unroll
             for (int r = 0; r < 8; ++r)
-              if (r < a.tp) add8<BF16>(acc3, x0[r]);
+              if (r < a.tp) {
+                if (a.slots_half) add8<false>(acc3, x0[r]);
+                else add8<BF16>(acc3, x0[r]);
+              }
           }
         } else if (MODE == 2) {
           const uint4* s = static_cast<const uint4*>(a.src) + 2 * i;
@@ -331,7 +335,9 @@ int launch_exchange(int mode, const void* src, void* mc_dst, void* const* peer_d
   a.vec = static_cast<size_t>(rows) * cols / 8;
   a.slot_units = static_cast<size_t>(slot_rows) * cols / 8;
   a.vec_per_row = cols / 8;
-  a.slots_f32 = slots_f32;
+  if (slots_f32 < 0 || slots_f32 > 2 || (slots_f32 == 2 && mode != 3)) return kErrInvalid;
+  a.slots_f32 = slots_f32 == 1;
+  a.slots_half = slots_f32 == 2;
   a.bias = static_cast<const uint16_t*>(bias);
   a.local_flags = a.peers.p[rank];
   a.tp = tp;

@@ -152,7 +152,9 @@ class FusedTensorParallelFFN:
     ``partial_dtype``: ``"fp32"`` (default) keeps every rank's partial sums in fp32 until they have been added, so the
     output is rounded to 16 bits once, as on one GPU, and meets the single-GPU error bound; ``"16bit"`` (the weight
     dtype) halves the bytes of the reduction, but every partial then carries its own rounding and a few outputs per
-    million end up just outside that bound (measured 1.0e-2 .. 1.3e-2 against 1e-2).
+    million end up just outside that bound (measured 1.0e-2 .. 1.3e-2 against 1e-2); ``"fp16"`` (push exchange) sends
+    the partial sums as fp16 whatever the weight dtype, clamped to the finite fp16 range: the bytes of ``"16bit"`` with
+    eight times finer rounding than bf16, for models whose down-projection outputs stay below 65504.
 
     The result of ``forward`` is a view of a symmetric buffer that peers write into: see ``forward``.
     """
@@ -171,10 +173,14 @@ class FusedTensorParallelFFN:
             raise ValueError("fused tensor-parallel FFN needs 2..8 ranks")
         if exchange not in ("push", "pipeline", "switch"):
             raise ValueError("exchange must be 'push', 'pipeline' or 'switch'")
-        if partial_dtype not in ("fp32", "16bit", "bf16", "fp16"):
-            raise ValueError("partial_dtype must be 'fp32' or '16bit'")
+        if partial_dtype not in ("fp32", "16bit", "fp16"):
+            raise ValueError("partial_dtype must be 'fp32', 'fp16' or '16bit'")
+        if partial_dtype == "fp16" and exchange != "push" and gate.dtype != torch.float16:
+            raise ValueError("partial_dtype='fp16' on a bf16 model needs exchange='push'")
         self.exchange = exchange
         self.partial_f32 = partial_dtype == "fp32"
+        # element type of the receive slots as the C calls name it: 0 weight dtype, 1 float, 2 fp16 whatever the weights are
+        self.slot_kind = 1 if self.partial_f32 else (2 if partial_dtype == "fp16" else 0)
         self.chunks = max(1, int(chunks)) if exchange != "push" else 1
         self.I, self.H = gate.shape
         g, u, d = shard_ffn_weights(gate, up, down, self.tp, self.rank)
@@ -192,7 +198,7 @@ class FusedTensorParallelFFN:
         self.pbytes = H * (4 if self.partial_f32 else 2)          # bytes per row of a partial-sum buffer
         VP = C.c_void_p * 8
         self._VP = VP
-        pdtype = torch.float32 if self.partial_f32 else self.dtype
+        pdtype = torch.float32 if self.partial_f32 else (torch.float16 if self.slot_kind == 2 else self.dtype)
         self._symm = symm_mem
 
         def ptrs(handle):
@@ -329,13 +335,13 @@ class FusedTensorParallelFFN:
             peer_slots = self._VP(*[(self.recv_ptrs[o] + self.rank * slot) if o < self.tp else None for o in range(8)])
             _lib.check("sfb200_sparse_gemm_scatter", L.sfb200_sparse_gemm_scatter(
                 hidden.data_ptr(), hidden.stride(0), self.dn.values.data_ptr(), self.dn.meta.data_ptr(),
-                self._cast(peer_slots), self.tp, mo, 1 if self.partial_f32 else 0, M, self.H, self.Ip, dt, st))
+                self._cast(peer_slots), self.tp, mo, self.slot_kind, M, self.H, self.Ip, dt, st))
             mark()
             self.epoch += 1
             peer_out = self._VP(*[(self.out_ptrs[d] + self.rank * blk) if d < self.tp else None for d in range(8)])
             mc = (self.mc_out + self.rank * blk) if self.out_multicast else None
             _lib.check("sfb200_tp_reduce_slots", L.sfb200_tp_reduce_slots(
-                self.recv.data_ptr(), self.slot_rows, 1 if self.partial_f32 else 0, mc, self._cast(peer_out), mo,
+                self.recv.data_ptr(), self.slot_rows, self.slot_kind, mc, self._cast(peer_out), mo,
                 self.H, dt, bias, flags, self.tp, self.rank, self.epoch, st))
             mark()
             self.kernel_launches += 3
