@@ -62,9 +62,11 @@ def parse_args():
                          "(push); the same movement as one light kernel per token chunk on a side stream beside the next "
                          "chunk's GEMMs (pipeline); the exchange pulled through NVSwitch (switch); NCCL all-reduce (nccl); "
                          "auto = push (the fastest of the four at 2 and 4 ranks with fp32 partial sums)")
-    ap.add_argument("--tp-partial", default="fp32", choices=["fp32", "fp16", "16bit"],
-                    help="N > 1, push / switch: type of the per-rank partial sums that are exchanged (16bit halves the bytes of "
-                         "the reduction but rounds every partial; see FusedTensorParallelFFN)")
+    ap.add_argument("--tp-partial", default="auto", choices=["auto", "fp32", "fp16", "16bit"],
+                    help="N > 1, push / pipeline / switch: type of the per-rank partial sums that are exchanged.  fp32 rounds "
+                         "once, after the sum; fp16 (push only) halves the bytes on the wire and still meets the single-GPU "
+                         "error bound (partial sums clamped to +-65504); 16bit = the weight dtype (bf16 partials miss the bound "
+                         "by a little).  auto = fp16 with push, else fp32")
     ap.add_argument("--tp-chunks", type=int, default=0, help="N > 1, pipeline / switch: token chunks (0 = 2 for pipeline, 1 for switch)")
     ap.add_argument("--tp-phases", action="store_true", help="N > 1: print per-phase device times to stderr")
     ap.add_argument("--chunks", type=int, default=1, help="token chunks for all-reduce overlap (N > 1, --tp nccl)")
@@ -546,6 +548,8 @@ def main():
     ffn = None
     if world > 1 and args.tp == "auto":
         args.tp = "push"
+    if args.tp_partial == "auto":
+        args.tp_partial = "fp16" if args.tp == "push" else "fp32"
     if world > 1 and args.tp in ("push", "pipeline", "switch"):
         try:
             chunks = args.tp_chunks or (2 if args.tp == "pipeline" else 1)

@@ -177,13 +177,15 @@ SFB200_API int sfb200_ffn_forward_host(const sfb200_ffn_weights* w, const void* 
  * Row-parallel GEMM with the reduce-scatter fused into its epilogue: rank r computes its partial
  * Y_r[M, N] = X_r . W_r^T and stores token block o (tok_per_owner tokens, a multiple of 16) straight into
  * peer_slots[o], rank o's receive slot for rank r ([tok_per_owner, N]), with plain stores over NVLink that overlap the
- * GEMM tile by tile.  peer_slots is a HOST array of tp device pointers.  tp <= 8.  slots_f32 selects the element type
+ * GEMM tile by tile.  peer_slots is a HOST array of tp device pointers.  tp <= 8.  `rank` is the caller's rank: its
+ * token tiles are visited starting at rank + 1's block, so that the ranks write to different owners at any one time
+ * instead of all to the same one.  slots_f32 selects the element type
  * of the slots, here and in the reduction calls below: 0 = `dtype`; 1 = float (the partial sums are rounded to 16 bits
  * only once, after they have been added); 2 = fp16 whatever `dtype` is, clamped to +-65504 (half the bytes of float on
  * the wire, 11 significant bits instead of bf16's 8: measured inside the single-GPU error bound where bf16 slots are not).
  */
 SFB200_API int sfb200_sparse_gemm_scatter(const void* x, int ldx, const void* values, const void* meta,
-                                          void* const* peer_slots, int tp, int tok_per_owner, int slots_f32, int M,
+                                          void* const* peer_slots, int tp, int rank, int tok_per_owner, int slots_f32, int M,
                                           int N, int K, int dtype, void* stream);
 /*
  * Second half, ONE launch per rank with the cross-GPU ordering inside the kernel: waits until every rank's GEMM has

@@ -72,7 +72,7 @@ def lib() -> C.CDLL:
     L.sfb200_silu_mul.argtypes = [vp, i, vp, i, vp, i, i, i, i, vp]
     L.sfb200_ffn_forward.argtypes = [C.POINTER(FFNWeights), vp, i, vp, vp, i, i, vp]
     L.sfb200_ffn_forward_host.argtypes = [C.POINTER(FFNWeights), vp, vp, i, vp]
-    L.sfb200_sparse_gemm_scatter.argtypes = [vp, i, vp, vp, C.POINTER(vp), i, i, i, i, i, i, i, vp]
+    L.sfb200_sparse_gemm_scatter.argtypes = [vp, i, vp, vp, C.POINTER(vp), i, i, i, i, i, i, i, i, vp]
     L.sfb200_tp_reduce_slots.argtypes = [vp, i, i, vp, C.POINTER(vp), i, i, i, vp, C.POINTER(vp), i, i, C.c_uint, vp]
     L.sfb200_tp_push_reduce.argtypes = [vp, i, C.POINTER(C.c_int), C.POINTER(vp), vp, i, i, C.POINTER(vp), i, i, i, vp,
                                         C.POINTER(vp), i, i, C.c_uint, i, vp]

@@ -343,7 +343,7 @@ int sfb200_ffn_forward_host(const sfb200_ffn_weights* w, const void* x_host, voi
 }
 
 int sfb200_sparse_gemm_scatter(const void* x, int ldx, const void* values, const void* meta,
-                               void* const* peer_slots, int tp, int tok_per_owner, int slots_f32, int M, int N, int K,
+                               void* const* peer_slots, int tp, int rank, int tok_per_owner, int slots_f32, int M, int N, int K,
                                int dtype, void* stream) {
   int err = kOk;
   DeviceState* s = device_state(&err);
@@ -367,10 +367,11 @@ int sfb200_sparse_gemm_scatter(const void* x, int ldx, const void* values, const
   a.act = kActNone;
   a.num_sms = s->num_sms;
   a.force_bn = s->force_bn;
-  if (slots_f32 < 0 || slots_f32 > 2) return kErrInvalid;
+  if (slots_f32 < 0 || slots_f32 > 2 || rank < 0 || rank >= tp) return kErrInvalid;
   a.out_f32 = slots_f32;
   a.peer_y = peer_slots;
   a.tp = tp;
+  a.rank = rank;
   a.tok_per_owner = tok_per_owner;
   if (a.force_bn < 1000 || (a.force_bn >= 3000 && a.force_bn < 5000)) a.force_bn = pick_pair_variant(N, M, K, s->num_sms, 0);
   return launch_sparse_gemm_pair(a, static_cast<cudaStream_t>(stream));

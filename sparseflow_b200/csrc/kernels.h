@@ -72,6 +72,7 @@ struct SparseGemmArgs {
   // peer_y: HOST array of tp device pointers (peer-mapped memory), or null.
   void* const* peer_y;
   int tp;
+  int rank;               // this rank (peer_y set): its token tiles are visited starting at the next rank's block
   int tok_per_owner;
 };
 int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream);

@@ -130,6 +130,8 @@ struct PairParams {
   void* peer_y[8];
   int band;            // tiles of the RESIDENT operand per L2 band (see tile_coords)
   int order;           // 0: activations resident (bands of token tiles); 1: weights resident (bands of row tiles)
+  int n_rot;           // token tiles are visited starting from this one (wrapping around): with the reduce-scatter in the
+                       // epilogue every rank starts at another owner's block, so no owner receives from all ranks at once
   int out_f32;         // store epilogue: 1 = y is float [m_tok, ldy], results stored unrounded; 2 = y is fp16 whatever
                        // the operand type, results clamped to the finite fp16 range (partial sums on their way to a sum)
 };
@@ -164,6 +166,8 @@ __device__ __forceinline__ void tile_coords(int tile, const PairParams& p, int& 
     n_blk = r / height;
     m_blk = b * p.band + (r - n_blk * height);
   }
+  n_blk += p.n_rot;
+  if (n_blk >= p.num_n_blks) n_blk -= p.num_n_blks;
 }
 
 int g_force_order = -1;  // tuning hook: -1 automatic, 0 / 1 force the tile order
@@ -742,6 +746,11 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
     p.tok_per_owner = a.tok_per_owner;
   }
   p.out_f32 = a.out_f32;
+  p.n_rot = 0;
+  if (a.peer_y != nullptr && a.tp > 1 && a.tok_per_owner > 0) {
+    const int first = ((a.rank + 1) % a.tp) * a.tok_per_owner / C::BN;   // the token tile where the next rank's block begins
+    p.n_rot = first < p.num_n_blks ? first : 0;
+  }
   pick_order(a.n_out, a.m_tok, a.K, C::ROWS_TILE, C::BN, p.num_m_blks, p.num_n_blks, p);
   if (g_force_order >= 0) {
     p.order = g_force_order;

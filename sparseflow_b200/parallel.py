@@ -335,7 +335,7 @@ class FusedTensorParallelFFN:
             peer_slots = self._VP(*[(self.recv_ptrs[o] + self.rank * slot) if o < self.tp else None for o in range(8)])
             _lib.check("sfb200_sparse_gemm_scatter", L.sfb200_sparse_gemm_scatter(
                 hidden.data_ptr(), hidden.stride(0), self.dn.values.data_ptr(), self.dn.meta.data_ptr(),
-                self._cast(peer_slots), self.tp, mo, self.slot_kind, M, self.H, self.Ip, dt, st))
+                self._cast(peer_slots), self.tp, self.rank, mo, self.slot_kind, M, self.H, self.Ip, dt, st))
             mark()
             self.epoch += 1
             peer_out = self._VP(*[(self.out_ptrs[d] + self.rank * blk) if d < self.tp else None for d in range(8)])
