@@ -356,7 +356,7 @@ int launch_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
 // Kernel / token-tile choice from 129 tokens up: the cheapest, by estimated time, of the single-CTA tiles and the
 // CTA-pair tiles.  Up to about a thousand tokens every candidate is bound by operand traffic, not by the tensor pipe,
 // and what decides is how many passes ("waves") the tile count needs on the available SMs (or SM pairs):
-//   single-CTA tile of bn tokens: waves x 64-wide K steps x step time + 4 us, where a step moves 9 KiB (values +
+//   single-CTA tile of bn tokens: waves x 64-wide K steps x step time + 8.5 us, where a step moves 9 KiB (values +
 //     metadata) + bn x 128 B (tokens), an SM sustains about 145 GB/s of operand traffic and all SMs together about
 //     19.5 TB/s out of L2 (17 TB/s for the 256-token tile, whose ring is only four stages deep);
 //   CTA-pair tiles: pick_pair_variant's estimate.
@@ -375,7 +375,7 @@ int pick_mid_variant(int n_out, int m_tok, int K, int num_sms, int swiglu) {
     const double active = tiles < num_sms ? static_cast<double>(tiles) : static_cast<double>(num_sms);
     const double bytes = 9216.0 + bn * 128.0;
     const double per_sm = bytes / 145e9, shared = active * bytes / (bn == 256 ? 17e12 : 19.5e12);
-    const double cost = (waves * k64 * (per_sm > shared ? per_sm : shared) + 4e-6) * 1e6;
+    const double cost = (waves * k64 * (per_sm > shared ? per_sm : shared) + 8.5e-6) * 1e6;
     if (cost < best) { best = cost; pick = bn; }
   }
   double pcost = 1e30;

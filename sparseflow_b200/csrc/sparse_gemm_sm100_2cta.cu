@@ -234,26 +234,24 @@ struct PairCfg {
   static constexpr int D_ROW_BYTES = (EPI == kEpiSwiGLU) ? 32 : 64;
   static constexpr int D_BUF_BYTES = 16 * D_ROW_BYTES;
   static constexpr int OFF_D = OFF_E + E_STAGES * E_BYTES;
-  // Epilogue warps: 4 lane quadrants x 2 (RS = 1) or x 4 (RS = 2).  The drain of a 16-column chunk is a chain of a few
-  // hundred dependent instructions, so what shortens it is more warps per scheduler, and the 512-row tiles, whose drain
-  // is not hidden behind the next tile's K loop, get sixteen (with one staging buffer each instead of two).
-  static constexpr int EPI_WARPS = (RS == 2) ? 16 : 8;
-  static constexpr int D_BUFS = (RS == 2) ? 1 : 2;
+  // Epilogue warps: 4 lane quadrants x 2 where the tile has two accumulator sets (its drain hides behind the next tile's
+  // K loop), x 4 where it has one (256 x 256 and the 512-row tiles: the MMA stream waits for the drain, and a 16-column
+  // chunk is a chain of a few hundred dependent instructions, so what shortens the drain is more warps per scheduler).
+  // The warps of a quadrant share the accumulator's 16-column chunks: RS = 2 -> one row set each, then halves.
+  static constexpr int EPI_WARPS = (ACC_BUFS == 1) ? 16 : 8;
+  static constexpr int D_BUFS = (EPI_WARPS == 16) ? 1 : 2;
   static constexpr int D_BYTES = EPI_WARPS * D_BUFS * D_BUF_BYTES;
   static constexpr int OFF_BAR = OFF_D + D_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
-  // RS = 1: the accumulator is drained in windows of 128 columns, [0, 128) and [BN - 128, BN), one per warp of a
-  // quadrant; the second window stores only what the first does not cover, i.e. it skips its first (256 - BN) / 16
-  // chunks.  RS = 2: the four warps of a quadrant take one accumulator (row set) and one half of its chunks each.
-  static constexpr int COLS_PER_WARP = 128;
-  static constexpr int SKIP_CHUNKS = (256 - BN) / 16;
-  static constexpr int PASSES = RS;
+  static constexpr int CHUNKS = BN / 16;
+  static constexpr int PARTS = EPI_WARPS / 4 / RS;                  // warps that share one accumulator's chunks
+  static constexpr int CHUNKS_PER_PART = (CHUNKS + PARTS - 1) / PARTS;
+  static_assert((PARTS - 1) * CHUNKS_PER_PART < CHUNKS, "every epilogue warp has at least one chunk");
   static_assert(RS == 1 || RS == 2, "RS");
   static_assert(BK == 128 || STAGES % 2 == 0, "BK = 64 needs an even stage count");
   static_assert(BN % 16 == 0 && BN <= 256 && BN >= 128, "BN");
   static_assert(HALF_N % 8 == 0, "token half must be whole swizzle atoms");
-  static_assert(COLS_PER_WARP % 16 == 0, "epilogue chunking");
   static_assert(TMEM_USED <= 512, "tmem");
   static_assert(SMEM_BYTES <= 232448, "smem");
 };
@@ -271,18 +269,9 @@ __device__ __forceinline__ float bias_at(const void* bias, int o, int fmt) {
   if (fmt == 1) return __uint_as_float(static_cast<uint32_t>(b) << 16);
   return __half2float(__ushort_as_half(b));
 }
-// 16 lanes x 128 columns: thread l gets, for repetition n (8 columns each), r[4n], r[4n+1] =
+// 16 lanes x 16 columns: thread l gets, for repetition n (8 columns each), r[4n], r[4n+1] =
 // (lane l/4, columns 8n + 2(l%4), +1) and r[4n+2], r[4n+3] = (lane l/4 + 8, same columns): the
-// accumulator-fragment layout of warp-level MMA, which stmatrix can transpose.
-__device__ __forceinline__ void tmem_ld_16x256b_x16(uint32_t taddr, uint32_t (&r)[64]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.16x256b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
-      : "r"(taddr)
-      : "memory");
-}
-// Same layout, 16 columns (two repetitions): 8 registers.
+// accumulator-fragment layout of warp-level MMA, which stmatrix can transpose.  Two repetitions: 8 registers.
 __device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)[8]) {
   asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
@@ -475,13 +464,12 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
   } else {
     // ------------------------------------------------------------ epilogue (warps 2 and up, both CTAs)
     const int q = warp & 3;                 // lane quadrant
-    const int w2 = (warp - 2) >> 2;         // RS = 1: 0 / 1 = column window; RS = 2: bit 0 = accumulator, bit 1 = chunk half
-    const int acc = (C::RS == 1) ? 0 : (w2 & 1);
-    const int col0 = (C::RS == 1) ? w2 * (C::BN - 128) : 0;
-    constexpr int kChunks = C::BN / 16, kHalf = (kChunks + 1) / 2;
-    // chunks [c_begin, c_end) of the window are this warp's to store
-    const int c_begin = (C::RS == 1) ? w2 * C::SKIP_CHUNKS : (w2 >> 1) * kHalf;
-    const int c_end = (C::RS == 1) ? 8 : ((w2 >> 1) ? kChunks : kHalf);
+    const int w2 = (warp - 2) >> 2;         // index of this warp among the warps of its quadrant
+    const int acc = (C::RS == 1) ? 0 : (w2 & 1);                    // row set
+    const int part = (C::RS == 1) ? w2 : (w2 >> 1);
+    // chunks [c_begin, c_end) of the accumulator are this warp's to store
+    const int c_begin = part * C::CHUNKS_PER_PART;
+    const int c_end = c_begin + C::CHUNKS_PER_PART < C::CHUNKS ? c_begin + C::CHUNKS_PER_PART : C::CHUNKS;
     const uint32_t leader_acce0 = mapa_u32(bar_acce, 0);
     const uint64_t pol_stream = l2_policy_evict_first();
     bool ok = true;
@@ -499,20 +487,14 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
       if (!ok) break;
       tc_fence_after();
       const int row_w = m_blk * C::ROWS_TILE + static_cast<int>(rank) * C::ROWS_CTA + acc * 128 + q * 32;
-      const int tok_w = n_blk * C::BN + col0;
-      const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * C::ACC_COLS + acc * C::BN + col0;
-      // Two forms of the drain.  The epilogue's code is executed once per tile by 8 warps that are out of step with
-      // one another, so a fully unrolled drain (thousands of instructions: 128 accumulator registers converted and
-      // stored one by one) runs out of the instruction cache: measured ~17 stall cycles per issued instruction and
-      // 15 - 25 us of epilogue per tile, which bounds every tile whose K loop is shorter than that.  Where the tile has
-      // TWO accumulator sets the drain is therefore a ROLLED loop over 16-column chunks (load, wait, convert, store;
-      // ~150 instructions), and the accumulator is handed back after the last chunk: the MMA stream is already filling
-      // the other set.  The 512-row tiles (RS = 2, one accumulator set of 2 x BN columns) use the rolled loop too: their
-      // unrolled drain stalled the whole SM on instruction fetches (measured on 4096 x 11008 at 2048 tokens: 35 stall
-      // cycles per issued instruction, tensor pipe active 28 %, 197 us; rolled 77 us), the producer and the MMA issuer
-      // included.  Only the 256 x 256 tile (one accumulator set, RS = 1) reads its accumulator into registers in one
-      // piece (unrolled) and hands it back before conversion and stores.
-      constexpr bool kRolled = C::ACC_BUFS == 2 || C::RS == 2;
+      const int tok_w = n_blk * C::BN;
+      const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * C::ACC_COLS + acc * C::BN;
+      // The drain is a ROLLED loop over 16-column chunks (load, wait, convert, store; ~150 instructions).  The epilogue's
+      // code is executed once per tile by warps that are out of step with one another, and a drain written out in full
+      // (128 accumulator registers converted and stored one by one, thousands of instructions) ran out of the
+      // instruction cache: measured 17-35 stall cycles per issued instruction for every warp of the SM, the TMA producer
+      // and the MMA issuer included (512 x 240 tile on 4096 x 11008 at 2048 tokens: tensor pipe active 28 %, 197 us;
+      // rolled 75 us).  The accumulator is handed back as soon as its last chunk is in registers.
       const int out_cols = (C::EPI == kEpiSwiGLU) ? p.n_out / 2 : p.n_out;
       const int g = lane >> 2;
       const uint32_t stage0 = sbase + C::OFF_D + (warp - 2) * C::D_BUFS * C::D_BUF_BYTES;
@@ -598,34 +580,15 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
       if (C::EPI == kEpiStore && p.out_f32 == 1) {
         const bool row_ok = row_w + lane < p.n_out;
         const float bias_v = (p.bias != nullptr && row_ok) ? bias_at(p.bias, row_w + lane, p.fmt) : 0.f;
-        if constexpr (kRolled) {
-          uint32_t r[16];
+        uint32_t r[16];
 #pragma unroll 1
-          for (int c = c_begin; c < c_end; ++c) {
-            tmem_ld_32x32b_x16(t_acc + 16 * c, r);
-            tmem_ld_wait();
-            const int t0 = tok_w + c * 16;
-            if (t0 < p.m_tok) store_chunk32(r, t0, bias_v, row_ok);
-          }
-          release_acc();
-        } else {
-          uint32_t vr[128];
-#pragma unroll
-          for (int ps = 0; ps < C::PASSES; ++ps) {
-            const int win = (C::RS == 1) ? 0 : ps * (C::BN - 128);
-            const int cb = (C::RS == 1) ? c_begin : ps * C::SKIP_CHUNKS;
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-              tmem_ld_32x32(t_acc + win + 32 * k, reinterpret_cast<uint32_t(&)[32]>(vr[32 * k]));
-            tmem_ld_wait();
-            if (ps == C::PASSES - 1) release_acc();
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              const int t0 = tok_w + win + c * 16;
-              if (c >= cb && t0 < p.m_tok) store_chunk32(&vr[16 * c], t0, bias_v, row_ok);
-            }
-          }
+        for (int c = c_begin; c < c_end; ++c) {
+          tmem_ld_32x32b_x16(t_acc + 16 * c, r);
+          tmem_ld_wait();
+          const int t0 = tok_w + c * 16;
+          if (t0 < p.m_tok) store_chunk32(r, t0, bias_v, row_ok);
         }
+        release_acc();
       } else {
         float b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;   // bias of rows g, g+8, 16+g, 24+g
         if (C::EPI == kEpiStore && p.bias != nullptr) {
@@ -634,43 +597,24 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
           if (row_w + g + 16 < p.n_out) b2 = bias_at(p.bias, row_w + g + 16, p.fmt);
           if (row_w + g + 24 < p.n_out) b3 = bias_at(p.bias, row_w + g + 24, p.fmt);
         }
-        if constexpr (kRolled) {
-          // two register sets in turn: the loads of chunk c + 1 are in flight while chunk c is converted and stored
-          uint32_t ra[8], rb[8], sa[8], sb[8];
-          auto load_chunk = [&](int c, uint32_t (&lo)[8], uint32_t (&hi)[8]) {
-            tmem_ld_16x256b_x2(t_acc + 16 * c, lo);                                          // lanes q*32 + 0..15
-            tmem_ld_16x256b_x2(t_acc + 16 * c + (static_cast<uint32_t>(16) << 16), hi);      // lanes q*32 + 16..31
-          };
-          load_chunk(c_begin, ra, rb);
+        // two register sets in turn: the loads of chunk c + 1 are in flight while chunk c is converted and stored
+        uint32_t ra[8], rb[8], sa[8], sb[8];
+        auto load_chunk = [&](int c, uint32_t (&lo)[8], uint32_t (&hi)[8]) {
+          tmem_ld_16x256b_x2(t_acc + 16 * c, lo);                                          // lanes q*32 + 0..15
+          tmem_ld_16x256b_x2(t_acc + 16 * c + (static_cast<uint32_t>(16) << 16), hi);      // lanes q*32 + 16..31
+        };
+        load_chunk(c_begin, ra, rb);
 #pragma unroll 1
-          for (int c = c_begin; c < c_end; c += 2) {
+        for (int c = c_begin; c < c_end; c += 2) {
+          tmem_ld_wait();
+          if (c + 1 < c_end) load_chunk(c + 1, sa, sb);
+          else release_acc();                                  // last chunk is in registers
+          store_chunk16(ra, rb, c, tok_w + c * 16, b0, b1, b2, b3);
+          if (c + 1 < c_end) {
             tmem_ld_wait();
-            if (c + 1 < c_end) load_chunk(c + 1, sa, sb);
-            else release_acc();                                  // last chunk is in registers
-            store_chunk16(ra, rb, c, tok_w + c * 16, b0, b1, b2, b3);
-            if (c + 1 < c_end) {
-              tmem_ld_wait();
-              if (c + 2 < c_end) load_chunk(c + 2, ra, rb);
-              else release_acc();
-              store_chunk16(sa, sb, c + 1, tok_w + (c + 1) * 16, b0, b1, b2, b3);
-            }
-          }
-        } else {
-          // both 16-lane halves of this warp's quadrant, one window of 128 columns, in the MMA-fragment layout; one
-          // wait per window; the accumulator is handed back after the LAST window's loads have landed
-          uint32_t va[64], vb[64];
-#pragma unroll
-          for (int ps = 0; ps < C::PASSES; ++ps) {
-            // window of this pass: RS = 1 -> chosen by w2 (already folded into t_acc / tok_w); RS = 2 -> by ps
-            const int win = (C::RS == 1) ? 0 : ps * (C::BN - 128);
-            const int cb = (C::RS == 1) ? c_begin : ps * C::SKIP_CHUNKS;
-            tmem_ld_16x256b_x16(t_acc + win, va);
-            tmem_ld_16x256b_x16(t_acc + win + (static_cast<uint32_t>(16) << 16), vb);
-            tmem_ld_wait();
-            if (ps == C::PASSES - 1) release_acc();
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-              if (c >= cb) store_chunk16(&va[8 * c], &vb[8 * c], c, tok_w + win + c * 16, b0, b1, b2, b3);
+            if (c + 2 < c_end) load_chunk(c + 2, ra, rb);
+            else release_acc();
+            store_chunk16(sa, sb, c + 1, tok_w + (c + 1) * 16, b0, b1, b2, b3);
           }
         }
       }
@@ -776,8 +720,9 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
 //     order, + 4 us of exposed drain per tile with the plain store epilogue (the SiLU.mul epilogue stores half as
 //     much and measured no exposed part): they win where K is long (4096 x 11008 at 4096 tokens 161 -> 145 us,
 //     4096 x 14336 210 -> 188 us, 8192 x 28672 834 -> 735 us) and tie on the gate|up shapes of K = 4096;
-//   256 x 256 with one accumulator set (1256): its unrolled drain runs out of the instruction cache and is exposed;
-//     since the 512-row tiles got their rolled drain it is never the fastest and is kept for forcing only;
+//   256 x 256 with one accumulator set (1256, sixteen epilogue warps): the 12xx K step at bn = 256 + an exposed drain of
+//     4 us (store) / 2 us (SiLU.mul) per tile; it wins where its 256-token tiles make one pass over the SM pairs and
+//     the others need two (4096 x 11008 at 1024 tokens: 64 tiles, 46 us against 64 us for the next best);
 //   launch, prologue, first fill and last drain: 8.5 us.
 // What decides in practice is the number of passes over the SM pairs.
 int pick_pair_variant_impl(int n_out, int m_tok, int K, int pairs, int swiglu, double* cost_us) {
@@ -794,6 +739,12 @@ int pick_pair_variant_impl(int n_out, int m_tok, int K, int pairs, int swiglu, d
   for (int bn : cands) {
     const double c = 8.5 + waves(rows256 * ((m_tok + bn - 1) / bn)) * k128 * (0.159 + 0.00102 * bn) * f12;
     if (c < best_cost * 0.985) { best_cost = c; best = 1000 + bn; }
+  }
+  {
+    const long t1 = rows256 * ((m_tok + 255) / 256);
+    const double crowd = t1 <= pairs ? 0.85 : 1.0;     // one, partly filled pass: measured 46 us on 4096 x 11008 at 1024 tokens
+    const double c = 8.5 + waves(t1) * (k128 * (0.159 + 0.00102 * 256) * f12 * crowd + (swiglu ? 2.0 : 4.0));
+    if (c < best_cost * 0.97) { best_cost = c; best = 1256; }
   }
   if (m_tok >= 1024 && n_out >= 1024) {
     double c5 = 1e300;

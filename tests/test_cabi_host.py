@@ -268,8 +268,10 @@ def test_kernel_plan_per_shape():
     assert plan(64, 22016, 4096, 1) == 64             # the SwiGLU epilogue has no split-K form
     # from 129 tokens: the cheapest of single-CTA tiles and CTA-pair tiles by estimated time (passes over the SMs)
     assert plan(512, 14336, 4096) == 1192 and plan(512, 22016, 4096, 1) == 1192 and plan(1024, 22016, 4096, 1) == 5208
-    assert plan(256, 14336, 4096) == 256 and plan(512, 4096, 14336) == 128 and plan(1024, 4096, 4096) == 256
-    assert plan(768, 4096, 11008) == 1192 and plan(768, 4096, 4096) == 192
+    assert plan(256, 4096, 4096) == 128 and plan(512, 4096, 14336) == 128 and plan(768, 4096, 11008) == 1192
+    # the 256 x 256 pair tile where it covers the output in ONE pass over the 74 SM pairs and the others need two
+    assert plan(1024, 4096, 4096) == 1256 and plan(1024, 4096, 11008) == 1256 and plan(512, 8192, 8192) == 1256
+    assert plan(256, 14336, 4096) == 1256
     # prefill: 256-row tiles with two accumulator sets where K is short (the drain hides behind the next tile), 512-row
     # tiles (the token tile is read by two row sets) where K is long or the passes over the SM pairs come out fewer
     assert plan(4096, 22016, 4096, 1) == 1240 and plan(4096, 4096, 4096) == 1240 and plan(2048, 22016, 4096, 1) == 5208
