@@ -523,40 +523,61 @@ __device__ __forceinline__ void pair_kernel_body(const CUtensorMap& tmA, const C
         __syncwarp();                                 // every lane has read this buffer's previous contents
         if (C::EPI == kEpiSwiGLU) {
           // half 0 = 16 gate rows, half 1 = the 16 matching up rows: pairing is in-thread
-          stmatrix_x4_trans(stage + st_off, pack16(silu_mul(a[0], b[0]), silu_mul(a[1], b[1]), p.fmt),
-                            pack16(silu_mul(a[2], b[2]), silu_mul(a[3], b[3]), p.fmt),
-                            pack16(silu_mul(a[4], b[4]), silu_mul(a[5], b[5]), p.fmt),
-                            pack16(silu_mul(a[6], b[6]), silu_mul(a[7], b[7]), p.fmt));
+          // (the output type is tested once per chunk, not once per value: the drain is a chain of dependent
+          // instructions and every branch inside it costs latency that nothing hides)
+          if (p.fmt == 1)
+            stmatrix_x4_trans(stage + st_off, pack16(silu_mul(a[0], b[0]), silu_mul(a[1], b[1]), 1),
+                              pack16(silu_mul(a[2], b[2]), silu_mul(a[3], b[3]), 1),
+                              pack16(silu_mul(a[4], b[4]), silu_mul(a[5], b[5]), 1),
+                              pack16(silu_mul(a[6], b[6]), silu_mul(a[7], b[7]), 1));
+          else
+            stmatrix_x4_trans(stage + st_off, pack16(silu_mul(a[0], b[0]), silu_mul(a[1], b[1]), 0),
+                              pack16(silu_mul(a[2], b[2]), silu_mul(a[3], b[3]), 0),
+                              pack16(silu_mul(a[4], b[4]), silu_mul(a[5], b[5]), 0),
+                              pack16(silu_mul(a[6], b[6]), silu_mul(a[7], b[7]), 0));
         } else {
           const bool half_out = p.out_f32 == 2;
-          const int of = half_out ? 0 : p.fmt;
-          auto f = [&](uint32_t v, float bias) {
-            const float r = act_fn(__uint_as_float(v) + bias, p.act);
-            return half_out ? fminf(fmaxf(r, -65504.f), 65504.f) : r;
+          // which conversion runs is tested once per chunk, not once per value: the drain is a chain of dependent
+          // instructions and every branch inside it costs latency that nothing hides
+          auto emit = [&](auto f, const int of) {
+            stmatrix_x4_trans(stage + st_off, pack16(f(a[0], b0), f(a[1], b0), of), pack16(f(a[2], b1), f(a[3], b1), of),
+                              pack16(f(a[4], b0), f(a[5], b0), of), pack16(f(a[6], b1), f(a[7], b1), of));
+            stmatrix_x4_trans(stage + st_off + 32, pack16(f(b[0], b2), f(b[1], b2), of),
+                              pack16(f(b[2], b3), f(b[3], b3), of), pack16(f(b[4], b2), f(b[5], b2), of),
+                              pack16(f(b[6], b3), f(b[7], b3), of));
           };
-          stmatrix_x4_trans(stage + st_off, pack16(f(a[0], b0), f(a[1], b0), of), pack16(f(a[2], b1), f(a[3], b1), of),
-                            pack16(f(a[4], b0), f(a[5], b0), of), pack16(f(a[6], b1), f(a[7], b1), of));
-          stmatrix_x4_trans(stage + st_off + 32, pack16(f(b[0], b2), f(b[1], b2), of),
-                            pack16(f(b[2], b3), f(b[3], b3), of), pack16(f(b[4], b2), f(b[5], b2), of),
-                            pack16(f(b[6], b3), f(b[7], b3), of));
+          if (p.act == kActNone && !half_out && p.fmt == 1) {          // bf16, no activation
+            emit([](uint32_t v, float bias) { return __uint_as_float(v) + bias; }, 1);
+          } else if (p.act == kActNone && half_out) {                   // partial sums on their way to a sum, as fp16
+            emit([](uint32_t v, float bias) { return fminf(fmaxf(__uint_as_float(v) + bias, -65504.f), 65504.f); }, 0);
+          } else {
+            const int of = half_out ? 0 : p.fmt;
+            emit([&](uint32_t v, float bias) {
+              const float r = act_fn(__uint_as_float(v) + bias, p.act);
+              return half_out ? fminf(fmaxf(r, -65504.f), 65504.f) : r;
+            }, of);
+          }
         }
         int tl;
         uint16_t* base = static_cast<uint16_t*>(chunk_dst(t0, tl));
         __syncwarp();
+        // lane -> (token of the chunk, 16-byte unit of its row); the second round is 32 / UNITS_PER_TOK tokens further on
         constexpr int UNITS_PER_TOK = C::D_ROW_BYTES / 16;          // 4 (store) or 2 (SiLU.mul)
+        constexpr int ROUNDS = UNITS_PER_TOK / 2, TOK_PER_ROUND = 32 / UNITS_PER_TOK;
+        const int tk0 = lane / UNITS_PER_TOK, part = lane % UNITS_PER_TOK;
+        const int col = out_x + part * 8;
+        uint16_t* dst = base + static_cast<size_t>(tl + tk0) * p.ldy + col;
+        const uint32_t src = stage + tk0 * C::D_ROW_BYTES + part * 16;
 #pragma unroll
-        for (int j = 0; j < UNITS_PER_TOK / 2; ++j) {
-          const int u = lane + 32 * j;
-          const int tk = u / UNITS_PER_TOK, part = u % UNITS_PER_TOK;
-          const int col = out_x + part * 8;
-          if (t0 + tk < p.m_tok && col < out_cols) {
+        for (int j = 0; j < ROUNDS; ++j) {
+          if (t0 + tk0 + j * TOK_PER_ROUND < p.m_tok && col < out_cols) {
             uint4 v;
             asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                          : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                         : "r"(stage + tk * C::D_ROW_BYTES + part * 16));
-            uint16_t* dst = base + static_cast<size_t>(tl + tk) * p.ldy + col;
-            asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(dst), "r"(v.x), "r"(v.y),
-                         "r"(v.z), "r"(v.w), "l"(pol_stream)
+                         : "r"(src + j * TOK_PER_ROUND * C::D_ROW_BYTES));
+            asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(
+                             dst + static_cast<size_t>(j * TOK_PER_ROUND) * p.ldy),
+                         "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "l"(pol_stream)
                          : "memory");
           }
         }
@@ -716,10 +737,10 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
 //     per doubling of K above 4096, up to 12 % (measured per step, 240-token tile: 0.404 us on 22016 x 4096, 0.43 - 0.44
 //     on 57344 x 8192 and 8192 x 8192, 0.45 - 0.47 on 4096 x 11008 / 14336, 0.48 on 8192 x 28672);
 //   512-row tiles (52xx: 3 stages of K = 128, one accumulator set of 2 x bn columns, sixteen epilogue warps): the token
-//     tile is written to shared memory once and read by two row sets, 0.27 + 0.00217 * bn us per K step whatever the
-//     order, + 4 us of exposed drain per tile with the plain store epilogue (the SiLU.mul epilogue stores half as
-//     much and measured no exposed part): they win where K is long (4096 x 11008 at 4096 tokens 161 -> 145 us,
-//     4096 x 14336 210 -> 188 us, 8192 x 28672 834 -> 735 us) and tie on the gate|up shapes of K = 4096;
+//     tile is written to shared memory once and read by two row sets, 0.247 + 0.00199 * bn us per K step whatever the
+//     order, + 4 us of exposed drain per tile with the plain store epilogue, 1.5 us with SiLU.mul (half as much to
+//     store): they win where K is long (4096 x 11008 at 4096 tokens 161 -> 142 us, 4096 x 14336 210 -> 188 us,
+//     8192 x 28672 834 -> 735 us) and tie on the gate|up shapes of K = 4096;
 //   256 x 256 with one accumulator set (1256, sixteen epilogue warps): the 12xx K step at bn = 256 + an exposed drain of
 //     4 us (store) / 2 us (SiLU.mul) per tile; it wins where its 256-token tiles make one pass over the SM pairs and
 //     the others need two (4096 x 11008 at 1024 tokens: 64 tiles, 46 us against 64 us for the next best);
@@ -752,7 +773,7 @@ int pick_pair_variant_impl(int n_out, int m_tok, int K, int pairs, int swiglu, d
     for (int bn : cands) {
       const long t2 = static_cast<long>((n_out + 511) / 512) * ((m_tok + bn - 1) / bn);
       const double crowd = t2 <= pairs ? 0.93 : 1.0;   // a single, partly filled pass: less contention for L2 (measured)
-      const double c = 8.5 + waves(t2) * (k128 * (0.27 + 0.00217 * bn) * crowd + (swiglu ? 0.0 : 4.0));
+      const double c = 8.5 + waves(t2) * (k128 * (0.247 + 0.00199 * bn) * crowd + (swiglu ? 1.5 : 4.0));
       if (c < c5 * 0.985) { c5 = c; b5 = 5000 + bn; }
     }
     if (c5 < best_cost * 0.98) { best_cost = c5; best = b5; }

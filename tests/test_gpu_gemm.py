@@ -201,6 +201,36 @@ def test_fp32_output_epilogue(bn, M):
     assert m["chain"] <= 1e-5 and m["floor"] <= 1e-3, m      # relative to the rms / to max(|ref|, 1e-2 rms)
 
 
+@pytest.mark.parametrize("kind", [0, 1, 2])
+@pytest.mark.parametrize("bn,rank", [(0, 0), (1240, 2), (5240, 1), (1256, 3)])
+def test_scatter_epilogue_slot_kinds_on_one_gpu(kind, bn, rank):
+    """sfb200_sparse_gemm_scatter with the four "owners'" receive slots in THIS GPU's memory (stores only, nothing waits):
+    token block o of the product lands in slot o, as the weight dtype (kind 0), float (1) or clamped fp16 (2), whatever
+    block the rank starts its token tiles at.  Rows of a slot beyond the block's live tokens stay untouched."""
+    import ctypes as C
+    from sparseflow_b200 import _lib
+    from sparseflow_b200.parallel import block_rows
+    dt, R, K, M, tp = "bf16", 1160, 1024 + 64, 1000, 4
+    w, x = seeded_weight(R, K, dt, 21), seeded_act(M, K, dt, 22)
+    cw = ops.compress_weight(to_dev(w, dt))
+    xd = to_dev(x, dt)
+    mo = block_rows(M, tp)
+    tdt = {0: torch.bfloat16, 1: torch.float32, 2: torch.float16}[kind]
+    slots = torch.full((tp, mo, R), 7.0, device="cuda", dtype=tdt)
+    ptrs = (C.c_void_p * 8)(*[slots[o].data_ptr() if o < tp else None for o in range(8)])
+    ops.force_token_tile(bn)
+    rc = _lib.lib().sfb200_sparse_gemm_scatter(xd.data_ptr(), K, cw.values.data_ptr(), cw.meta.data_ptr(),
+                                               C.cast(ptrs, C.POINTER(C.c_void_p)), tp, rank, mo, kind, M, R, K, ops.BF16,
+                                               torch.cuda.current_stream().cuda_stream)
+    ops.force_token_tile(0)
+    assert rc == 0 and ops.device_status() == 0
+    ref = o.gemm_ref(x, o.prune_24(w, dt)["pruned"], dt)
+    got = slots.float().cpu().numpy().reshape(tp * mo, R)
+    m = o.rel_err_metrics(got[:M], ref)
+    assert m["floor"] <= (1e-3 if kind == 1 else REL_TOL), m
+    assert (got[M:] == 7.0).all()          # the dead rows of the last owner's slot
+
+
 def test_config1_fp16_m512_k4096_n4096():
     y, ref = _run(4096, 4096, 512, "f16", wseed=1, xseed=1234)
     m = o.rel_err_metrics(y, ref)
