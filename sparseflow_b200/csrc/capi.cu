@@ -373,7 +373,9 @@ int sfb200_sparse_gemm_scatter(const void* x, int ldx, const void* values, const
   a.tp = tp;
   a.rank = rank;
   a.tok_per_owner = tok_per_owner;
-  if (a.force_bn < 1000 || (a.force_bn >= 3000 && a.force_bn < 5000)) a.force_bn = pick_pair_variant(N, M, K, s->num_sms, 0);
+  // a forced variant of another kernel family means nothing here: let the pair launcher choose (it keeps to the tiles
+  // with two accumulator sets, whose drain -- here stores over NVLink -- hides behind the next tile's K loop)
+  if (a.force_bn < 1000 || (a.force_bn >= 3000 && a.force_bn < 5000)) a.force_bn = 0;
   return launch_sparse_gemm_pair(a, static_cast<cudaStream_t>(stream));
 }
 

@@ -746,7 +746,7 @@ int launch_pair_cfg(const SparseGemmArgs& a, cudaStream_t stream) {
 //     the others need two (4096 x 11008 at 1024 tokens: 64 tiles, 46 us against 64 us for the next best);
 //   launch, prologue, first fill and last drain: 8.5 us.
 // What decides in practice is the number of passes over the SM pairs.
-int pick_pair_variant_impl(int n_out, int m_tok, int K, int pairs, int swiglu, double* cost_us) {
+int pick_pair_variant_impl(int n_out, int m_tok, int K, int pairs, int swiglu, double* cost_us, bool hidden_drain = false) {
   const double k128 = (K + 127) / 128;
   const double dbl = k128 > 32.0 ? std::log2(k128 / 32.0) : 0.0;
   const double fk = 1.0 + 0.08 * (dbl < 1.5 ? dbl : 1.5);
@@ -761,13 +761,14 @@ int pick_pair_variant_impl(int n_out, int m_tok, int K, int pairs, int swiglu, d
     const double c = 8.5 + waves(rows256 * ((m_tok + bn - 1) / bn)) * k128 * (0.159 + 0.00102 * bn) * f12;
     if (c < best_cost * 0.985) { best_cost = c; best = 1000 + bn; }
   }
-  {
+  // hidden_drain: only tiles whose drain hides behind the next tile's K loop (the drain stores over NVLink)
+  if (!hidden_drain) {
     const long t1 = rows256 * ((m_tok + 255) / 256);
     const double crowd = t1 <= pairs ? 0.85 : 1.0;     // one, partly filled pass: measured 46 us on 4096 x 11008 at 1024 tokens
     const double c = 8.5 + waves(t1) * (k128 * (0.159 + 0.00102 * 256) * f12 * crowd + (swiglu ? 2.0 : 4.0));
     if (c < best_cost * 0.97) { best_cost = c; best = 1256; }
   }
-  if (m_tok >= 1024 && n_out >= 1024) {
+  if (!hidden_drain && m_tok >= 1024 && n_out >= 1024) {
     double c5 = 1e300;
     int b5 = 0;
     for (int bn : cands) {
@@ -787,7 +788,7 @@ int dispatch_pair(const SparseGemmArgs& a, cudaStream_t stream) {
   // force_bn: 1256 / 1240 / 1224 / 1208 / 1192 = 256-row tiles with that many tokens;
   // 2192 / 2208 / 2224 / 2240 = 512-row tiles with that many tokens.  0 = automatic.
   int v = a.force_bn;
-  if (v == 0) v = pick_pair_variant_impl(a.n_out, a.m_tok, a.K, a.num_sms / 2, EPI == kEpiSwiGLU, nullptr);
+  if (v == 0) v = pick_pair_variant_impl(a.n_out, a.m_tok, a.K, a.num_sms / 2, EPI == kEpiSwiGLU, nullptr, a.peer_y != nullptr);
   switch (v) {
     case 1256: return launch_pair_cfg<PairCfg<256, 128, 4, 1, EPI>>(a, stream);
     case 1240: return launch_pair_cfg<PairCfg<240, 128, 4, 1, EPI>>(a, stream);
