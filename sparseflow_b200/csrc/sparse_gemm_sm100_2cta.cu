@@ -14,10 +14,11 @@
 //     columns of which the metadata ring needs 16-32.  With RS = 1 and BN <= 240 two accumulators
 //     fit (2 x 240 + 16 = 496): the MMA stream of tile i+1 fills one while the epilogue drains the
 //     other, so the epilogue is off the critical path.  BN = 256 and the RS = 2 tiles have a single
-//     accumulator set; their epilogue hands it back right after its last tensor-memory load and
-//     only its conversion and stores overlap the next tile's main loop.
+//     accumulator set: the MMA stream waits for their drain, which is therefore spread over sixteen
+//     warps instead of eight.
 //
-// 10 warps: warp 0 = TMA producer, warp 1 = MMA issuer / tensor-memory owner, warps 2..9 = epilogue.
+// Warps: warp 0 = TMA producer, warp 1 = MMA issuer / tensor-memory owner, warps 2 and up = epilogue
+// (8 or 16).  The drain is one rolled loop over 16-column chunks for every tile.
 // All loads are plain per-CTA TMA copies; nothing here reads another GPU's memory.
 #include <cmath>
 #include <cuda.h>
