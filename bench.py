@@ -62,7 +62,7 @@ def parse_args():
                     help="N > 1: reduce-scatter by peer stores in the down GEMM's epilogue + one reduce/all-gather kernel "
                          "(push); the same movement as one light kernel per token chunk on a side stream beside the next "
                          "chunk's GEMMs (pipeline); the exchange pulled through NVSwitch (switch); NCCL all-reduce (nccl); "
-                         "auto = push (the fastest of the four at 2 and 4 ranks with fp32 partial sums)")
+                         "auto = push (the fastest of the four at 2, 4 and 8 ranks)")
     ap.add_argument("--tp-partial", default="auto", choices=["auto", "fp32", "fp16", "16bit"],
                     help="N > 1, push / pipeline / switch: type of the per-rank partial sums that are exchanged.  fp32 rounds "
                          "once, after the sum; fp16 (push only) halves the bytes on the wire and still meets the single-GPU "
@@ -569,10 +569,14 @@ def main():
         except Exception as exc:      # symmetric memory unavailable on this box: NCCL path
             sys.stderr.write(f"fused tensor-parallel path unavailable ({exc!r}); using NCCL all-reduce\n")
             ffn = None
+            if args.tp_partial == "fp16":        # no fp16 wire format in the NCCL form: keep the error bound with fp32
+                args.tp_partial = "fp32"
     if ffn is None:
-        ffn = parallel.TensorParallelFFN(wg, wu, wd, chunks=args.chunks)
+        nccl_f32 = world > 1 and args.tp_partial == "fp32" and args.chunks == 1
+        ffn = parallel.TensorParallelFFN(wg, wu, wd, chunks=args.chunks, partial_dtype="fp32" if nccl_f32 else "16bit")
         if world > 1:
-            exchange = f"NCCL all-reduce after the down GEMM, {args.chunks} chunk(s)"
+            exchange = (f"NCCL all-reduce of {'fp32 partial sums' if nccl_f32 else 'the 16-bit output'} after the down GEMM, "
+                        f"{args.chunks} chunk(s)")
     fused_tp = isinstance(ffn, parallel.FusedTensorParallelFFN)
     del wg, wu
     hidden = torch.empty((M, ffn.Ip), dtype=dt, device=dev)

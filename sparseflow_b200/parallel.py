@@ -75,11 +75,20 @@ def unshard_hidden(parts: List[torch.Tensor], I: int) -> torch.Tensor:
 
 
 class TensorParallelFFN:
-    """Per-rank state of the TP FFN on the CUDA kernels."""
+    """Per-rank state of the TP FFN on the CUDA kernels, the exchange being one NCCL all-reduce of the down GEMM's
+    output: of the 16-bit output (``partial_dtype="16bit"``, the usual baseline: every rank's partial sum is rounded
+    before the sum) or, unchunked, of fp32 partial sums that are rounded once after the sum (``"fp32"``: twice the bytes
+    on the wire, the single-GPU error bound)."""
 
     def __init__(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, group=None,
-                 chunks: int = 1, down_bias: Optional[torch.Tensor] = None):
+                 chunks: int = 1, down_bias: Optional[torch.Tensor] = None, partial_dtype: str = "16bit"):
         from . import ops
+        if partial_dtype not in ("16bit", "fp32"):
+            raise ValueError("partial_dtype must be '16bit' or 'fp32'")
+        if partial_dtype == "fp32" and chunks > 1:
+            raise ValueError("fp32 partial sums are not chunked")
+        self.partial_f32 = partial_dtype == "fp32"
+        self._partial = None
         self.ops = ops
         self.group = group
         self.tp = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -103,6 +112,19 @@ class TensorParallelFFN:
         if out is None:
             out = torch.empty((M, self.H), dtype=x.dtype, device=x.device)
         bias = self.down_bias if self.rank == 0 else None      # added once across the sum
+        if self.partial_f32 and self.tp > 1:
+            from . import _lib
+            ops.sparse_gemm_swiglu(x, self.gu, out=hidden)
+            if self._partial is None or self._partial.shape[0] < M:
+                self._partial = torch.empty((M, self.H), dtype=torch.float32, device=x.device)
+            part = self._partial[:M]
+            _lib.check("sfb200_sparse_gemm_f32out", _lib.lib().sfb200_sparse_gemm_f32out(
+                hidden.data_ptr(), hidden.stride(0), self.dn.values.data_ptr(), self.dn.meta.data_ptr(), part.data_ptr(),
+                self.H, M, self.H, self.Ip, ops._dt(x), bias.data_ptr() if bias is not None else None, 0, ops._stream()))
+            self.kernel_launches += 2
+            dist.all_reduce(part, group=self.group)
+            out.copy_(part)                       # the one rounding to 16 bits
+            return out
         if self.chunks == 1 or self.tp == 1:
             ops.sparse_gemm_swiglu(x, self.gu, out=hidden)
             ops.sparse_gemm(hidden, self.dn, bias=bias, out=out)

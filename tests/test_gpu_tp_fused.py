@@ -67,6 +67,8 @@ def _worker(rank, world, port, ret):
         nccl = parallel.TensorParallelFFN(wg, wu, wd).forward(x).clone()
         res["nccl"] = chain(nccl)
         res["nccl_bias"] = chain(parallel.TensorParallelFFN(wg, wu, wd, down_bias=bias).forward(x), ref_b)
+        res["nccl_fp32"] = chain(parallel.TensorParallelFFN(wg, wu, wd, partial_dtype="fp32").forward(x))
+        res["nccl_fp32_bias"] = chain(parallel.TensorParallelFFN(wg, wu, wd, down_bias=bias, partial_dtype="fp32").forward(x), ref_b)
         # ---- push exchange, fp32 partial sums (the default)
         push = F(wg, wu, wd, max_tokens=M)
         a = push.forward(x).clone()
@@ -143,6 +145,7 @@ def test_tensor_parallel_ffn_two_gpus_against_oracle():
         r = got[rank]
         assert r["status"] == 0
         assert r["nccl"] <= 1.5e-2 and r["nccl_bias"] <= 1.5e-2, r
+        assert r["nccl_fp32"] <= 1e-2 and r["nccl_fp32_bias"] <= 1e-2, r      # all-reduce of fp32 partial sums: rounded once
         assert r["push"] <= 1e-2 and r["push_small"] <= 1e-2 and r["push_bias"] <= 1e-2, r       # fp32 partial sums
         assert r["push_repeat"] and r["push_shards"] and r["push_out_arg"], r
         assert r["pipeline1"] and r["pipeline3"] and r["pipeline1_small"] and r["pipeline3_small"] and r["pipeline_chunks"] >= 2, r
