@@ -291,13 +291,13 @@ SFB200_API int sfb200_blob_read_header(const void* header_host, size_t available
 /* Tuning hook: force the kernel variant / token tile on the current device.  0 = automatic;
  * 8 = decode kernel (M <= 32); 32/64/128/192/256 = single-CTA kernel with that token tile; 1256 =
  * CTA-pair kernel, 256-row x 256-token tiles; 1192/1208/1224/1240 = the same with that many tokens and
- * two accumulator sets; 2192/2208/2224/2240 = CTA-pair kernel, 512-row tiles
- * with that many tokens; 3032/3064/3128 and 4032/4064/4128 = split-K cluster kernel with 2 or 4
+ * two accumulator sets; 5192/5208/5224/5240 = CTA-pair kernel, 512-row tiles with that many tokens and
+ * 128-wide K stages (2192..2240: the same with 64-wide stages); 3032/3064/3128 and 4032/4064/4128 = split-K cluster kernel with 2 or 4
  * K slices and a 32/64/128-token tile.  No counterpart upstream. */
 SFB200_API int sfb200_debug_force_token_tile(int bn);
 
 /* Tuning hooks of the prefill kernel's tile order (process-wide; no counterpart upstream): l2_band_mb > 0 sets
- * the budget, in MB, of the band of the operand that is kept L2-resident (default 40); force_order picks that
+ * the budget, in MB, of the band of the operand that is kept L2-resident (default 56); force_order picks that
  * operand: -1 automatic (the smaller of activations and compressed weight), 0 activations, 1 weights. */
 SFB200_API int sfb200_debug_pair_tuning(int l2_band_mb, int force_order);
 

@@ -76,18 +76,19 @@ struct SparseGemmArgs {
   int tok_per_owner;
 };
 int launch_sparse_gemm(const SparseGemmArgs& a, cudaStream_t stream);
-// CTA-pair (cta_group::2) variant, 256-row x 256-token tiles; chosen by launch_sparse_gemm for
-// m_tok >= kPairMinTokens.  force_bn 1192..1256 (256-row tiles) or 2192..2240 (512-row tiles) picks a variant.
+// CTA-pair (cta_group::2) kernel; launch_sparse_gemm goes straight to it from 4 * kPairMinTokens tokens and weighs it
+// against the single-CTA tiles below that.  force_bn 1192..1256 (256-row tiles), 5192..5240 (512-row tiles, 128-wide
+// K stages) or 2192..2240 (512-row tiles, 64-wide stages) picks a variant.
 int launch_sparse_gemm_pair(const SparseGemmArgs& a, cudaStream_t stream);
 constexpr int kPairMinTokens = 1024;
 // Tuning hooks of the CTA-pair kernel's tile order: budget (MB) of the L2-resident operand's band (<= 0: keep),
 // and which operand is resident (-1 automatic, 0 activations, 1 weights).  Process-wide.
 void set_pair_tuning(int l2_band_mb, int force_order);
-// Variant the CTA-pair launcher picks on its own (1192..1240 or 5192..5240; swiglu: the SiLU.mul epilogue) and,
+// Variant the CTA-pair launcher picks on its own (1192..1256 or 5192..5240; swiglu: the SiLU.mul epilogue) and,
 // optionally, its estimated time in us.
 int pick_pair_variant(int n_out, int m_tok, int K, int num_sms, int swiglu, double* cost_us = nullptr);
 // The kernel variant launch_sparse_gemm runs for a shape when nothing is forced, in the numbering of
-// SparseGemmArgs::force_bn: 8 decode kernel; 32..256 single-CTA kernel with that token tile; 1192..1256 / 2192..2240
+// SparseGemmArgs::force_bn: 8 decode kernel; 32..256 single-CTA kernel with that token tile; 1192..1256 / 5192..5240
 // CTA-pair kernel; 3000 + tile / 4000 + tile split-K cluster kernel with 2 / 4 K slices.  Host-only.
 int plan_sparse_gemm(int m_tok, int n_out, int K, int epi, int num_sms);
 // The exchange step (reduction + all-gather) of the row-parallel GEMM in one launch per rank, cross-GPU ordering
