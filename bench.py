@@ -639,7 +639,8 @@ def main():
     clocks = sampler.summary(region_t0, region_t1)
     launches = ffn.kernel_launches - launches0
     result = out if not fused_tp else res
-    if fused_tp and args.tp_phases:       # after the timed region: ten more steps with events between the phases
+    tp_phase_ms = None
+    if fused_tp:       # after the timed region: ten more steps with events between the phases (every rank takes part)
         names = ["gate_up_gemm", "down_gemm_first_chunk", "exchange_and_remaining_chunks"]
         acc = [0.0] * len(names)
         for _ in range(10):
@@ -648,7 +649,11 @@ def main():
             torch.cuda.synchronize()
             for i in range(len(names)):
                 acc[i] += evs[i].elapsed_time(evs[i + 1]) / 10
-        sys.stderr.write(f"rank {rank} phases (ms): " + ", ".join(f"{n} {t:.4f}" for n, t in zip(names, acc)) + "\n")
+        if args.tp_phases:
+            sys.stderr.write(f"rank {rank} phases (ms): " + ", ".join(f"{n} {t:.4f}" for n, t in zip(names, acc)) + "\n")
+        pm = torch.tensor(acc, dtype=torch.float64, device=dev)
+        dist.all_reduce(pm, op=dist.ReduceOp.MAX)
+        tp_phase_ms = [float(v) for v in pm.tolist()]
         result = ffn.forward(x)
     ops.device_status()
     ms_total = s0.elapsed_time(s1)
@@ -691,6 +696,18 @@ def main():
                 "down_kernel": {"ms_per_launch": dn_ms, "achieved": dn_achieved, "frac": dn_achieved / peak,
                                 "variant": args.tile_down or args.tile or plan(M, H, I, 0, nsm)},
                 "ffn_frac": value / peak}
+    elif tp_phase_ms is not None:
+        # N > 1: the dominant kernel is still the gate|up GEMM, now of this rank's rows; timed in the phase steps
+        # above (max over ranks), against ONE GPU's peak
+        gu_ms = tp_phase_ms[0]
+        achieved = 2.0 * M * (2 * ffn.Ip) * H / (gu_ms * 1e-3) / 1e12
+        peak = 2.0 * burst
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": None, "kernel": f"sparse_gemm_pair_kernel, SiLU.mul epilogue (gate|up rows of one rank: {2 * ffn.Ip} x {H})",
+                "peak_source": f"2 x bf16_tflops ({src}); of {'measured' if src == 'measured' else 'fallback'}; per GPU",
+                "ms_per_launch": gu_ms, "per": "rank, max over ranks, from ten extra steps with events between the phases",
+                "phases_ms": dict(zip(["gate_up_gemm", "down_gemm_and_scatter", "exchange"], tp_phase_ms)),
+                "ffn_frac": value / (peak * world)}
 
     # ---- end to end with host buffers (H2D of x, FFN, D2H of out, every step)
     e2e = None
