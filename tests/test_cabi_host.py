@@ -278,3 +278,32 @@ def test_kernel_plan_per_shape():
     assert plan(4096, 4096, 11008) == 5240 and plan(4096, 4096, 14336) == 5240 and plan(2048, 4096, 11008) == 5240
     assert plan(8192, 57344, 8192, 1) == 5240 and plan(8192, 8192, 28672) == 5224 and plan(16384, 8192, 8192) == 5240
     assert plan(0, 4096, 4096) == 0
+
+
+def test_kernel_plan_is_always_a_known_variant():
+    """Every shape gets a variant the dispatcher knows, and the families keep to their token ranges: decode kernel up to
+    4 tokens, split-K cluster kernel up to 128, 512-row pair tiles from 1024."""
+    from sparseflow_b200 import _lib
+    plan = _lib.lib().sfb200_debug_plan_gemm
+    single = {32, 64, 128, 192, 256}
+    pair = {1192, 1208, 1224, 1240, 1256}
+    pair512 = {5192, 5208, 5224, 5240}
+    splitk = {3032, 3064, 3128, 4032, 4064, 4128}
+    for sms in (148, 132, 64):
+        for (N, K) in ((4096, 4096), (22016, 4096), (4096, 11008), (28672, 4096), (4096, 14336), (8192, 8192), (57344, 8192),
+                       (8192, 28672), (1024, 1024), (512, 256), (5504, 4096), (4096, 2752)):
+            for M in (1, 2, 4, 5, 16, 33, 64, 100, 128, 129, 200, 256, 500, 512, 768, 1000, 1024, 1500, 2048, 3000, 4096,
+                      8192, 16384, 40000):
+                for sw in (0, 1):
+                    if sw and N % 32:
+                        continue
+                    v = plan(M, N, K, sw, sms)
+                    assert v == 8 or v in single | pair | pair512 | splitk, (M, N, K, sw, sms, v)
+                    if v == 8:
+                        assert M <= 4
+                    if v in splitk:
+                        assert M <= 128 and sw == 0
+                    if v in pair512:
+                        assert M >= 1024
+                    if M >= 4096:
+                        assert v in pair | pair512
